@@ -1,0 +1,72 @@
+// Host-side interface of the bf16 tensor-core GEMM (tcgen05 + TMEM + TMA).
+//
+// Replaces the reference's cuBLAS SGEMM call sites (csrc/cuda/ops/matmul.cu:92-195):
+// one kernel covers matmul, bmm and every transposed form backward needs, so no
+// transposed copy is ever materialised (the reference transposes in
+// lua/luatorch/autograd.lua:105-114).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lt {
+
+enum GemmAct : int {
+  GEMM_ACT_NONE = 0,
+  GEMM_ACT_GELU = 1,    // out = gelu(acc + bias); optional aux_out receives acc + bias
+  GEMM_ACT_DGELU = 2,   // out = acc * gelu'(aux_in)
+  GEMM_ACT_RELU = 3,    // out = max(acc + bias, 0)
+  GEMM_ACT_DRELU = 4,   // out = acc * (aux_in > 0)
+};
+
+// C[b] = act(alpha * op(A[b]) * op(B[b]) + bias) + residual (+ C[b] if accumulate)
+//
+// Operand layouts (bf16, innermost stride 1):
+//   a_mn_major == 0 : A stored [M, K] with row stride lda      ("K-major")
+//   a_mn_major == 1 : A stored [K, M] with row stride lda      ("M-major", i.e. A^T in memory)
+//   b_mn_major == 0 : B stored [N, K] with row stride ldb      ("K-major", i.e. B^T in memory)
+//   b_mn_major == 1 : B stored [K, N] with row stride ldb      ("N-major", plain row-major B)
+// Batches are addressed with two nested batch indices (inner count `batch_inner`,
+// outer count `batch_outer`) so that [B, S, H, d]-strided attention operands need
+// no re-layout; element strides per operand.
+struct GemmArgs {
+  int M = 0, N = 0, K = 0;
+  const void* A = nullptr;
+  const void* B = nullptr;
+  void* C = nullptr;
+  int64_t lda = 0, ldb = 0, ldc = 0;
+  int a_mn_major = 0, b_mn_major = 1;
+  int batch_inner = 1, batch_outer = 1;
+  int64_t a_stride_inner = 0, a_stride_outer = 0;
+  int64_t b_stride_inner = 0, b_stride_outer = 0;
+  int64_t c_stride_inner = 0, c_stride_outer = 0;
+  float alpha = 1.0f;
+  int c_fp32 = 0;        // output element type: 0 bf16, 1 fp32
+  int accumulate = 0;    // C += result
+  const void* bias = nullptr;  // [N]
+  int bias_fp32 = 0;
+  int act = GEMM_ACT_NONE;
+  const void* residual = nullptr;  // bf16 [M, N], row stride ldr (unbatched use)
+  int64_t ldr = 0;
+  void* aux_out = nullptr;         // bf16 [M, N] pre-activation, row stride ldc
+  const void* aux_in = nullptr;    // bf16 [M, N] pre-activation for DGELU/DRELU, row stride ld_aux
+  int64_t ld_aux = 0;
+  int causal_tiles = 0;  // 1: skip output tiles strictly above the diagonal (n0 > m0 + BM - 1);
+                         // 2: skip tiles strictly below (m0 > n0 + BN - 1)
+};
+
+// Returns cudaSuccess or the launch error. Uses the tensor-core path whenever the
+// operands satisfy TMA alignment (base 16 B aligned, lda/ldb multiples of 8
+// elements); otherwise a SIMT fallback handles the call.
+cudaError_t gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+
+// True if `args` is eligible for the tcgen05 path.
+bool gemm_uses_tensor_cores(const GemmArgs& args);
+
+// Device-side status word written by bounded waits (0 = ok). Reading synchronises.
+int gemm_last_device_error();
+void gemm_clear_device_error();
+
+// Number of kernel launches issued by this translation unit since process start.
+uint64_t gemm_launch_count();
+
+}  // namespace lt

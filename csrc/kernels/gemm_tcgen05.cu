@@ -1,0 +1,657 @@
+// bf16 GEMM on the 5th-generation tensor cores: tcgen05.mma issued by one thread per
+// CTA, operands staged in shared memory by TMA (128-byte swizzle), fp32 accumulators
+// in TMEM, epilogue read back with tcgen05.ld.
+//
+// Structure: persistent kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer (one lane issues the tiled loads of each k-block)
+//   warp 1      TMEM owner + MMA issuer (one lane)
+//   warps 2..5  epilogue: each owns one 32-lane TMEM quadrant of the 128-row tile
+// The TMEM accumulator is double buffered (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// This kernel stands in for the reference's cublasSgemm / cublasSgemmStridedBatched
+// (csrc/cuda/ops/matmul.cu:121-133, 177-187) and for its add_broadcast / gelu_bias
+// kernels (csrc/cuda/ops/arithmetic.cu:478-484, csrc/cuda/ops/fused.cu:26-35), which
+// become epilogue options here.
+#include "gemm.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda.h>
+#include <atomic>
+#include <mutex>
+#include <stdio.h>
+
+namespace lt {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+template <int BN>
+struct TileCfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;   // 4 at BN=256, 6 at BN=128
+  static constexpr int TMEM_COLS = 2 * BN >= 32 ? 2 * BN : 32;  // power of two for 64/128/256
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ int g_gemm_error = 0;
+
+struct KernelParams {
+  int M, N, K;
+  int tiles_m, tiles_n, batch_inner, batch_total;
+  int a_mn, b_mn;
+  void* C;
+  long long ldc, c_stride_inner, c_stride_outer;
+  float alpha;
+  int c_fp32, accumulate;
+  const void* bias;
+  int bias_fp32;
+  int act;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  __nv_bfloat16* aux_out;
+  const __nv_bfloat16* aux_in;
+  long long ld_aux;
+  int causal_tiles;
+  int vec_ok;  // C / residual / aux rows allow 16-byte vector access
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+  const float k0 = 0.7978845608f, k1 = 0.044715f;
+  float t = tanh_fast(k0 * (x + k1 * x * x * x));
+  return 0.5f * x * (1.0f + t);
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+  const float k0 = 0.7978845608f, k1 = 0.044715f;
+  float t = tanh_fast(k0 * (x + k1 * x * x * x));
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k0 * (1.0f + 3.0f * k1 * x * x);
+}
+
+// Scalar epilogue for one element, shared by the tensor-core tail path and the SIMT
+// fallback kernel.
+__device__ __forceinline__ void epilogue_store_scalar(const KernelParams& p, char* c_base,
+                                                      long long row, int col, float acc) {
+  float v = acc * p.alpha;
+  if (p.bias) {
+    v += p.bias_fp32 ? ((const float*)p.bias)[col]
+                     : __bfloat162float(((const __nv_bfloat16*)p.bias)[col]);
+  }
+  if (p.act == GEMM_ACT_GELU) {
+    if (p.aux_out) p.aux_out[row * p.ldc + col] = __float2bfloat16(v);
+    v = gelu_f(v);
+  } else if (p.act == GEMM_ACT_RELU) {
+    if (p.aux_out) p.aux_out[row * p.ldc + col] = __float2bfloat16(v);
+    v = fmaxf(v, 0.0f);
+  } else if (p.act == GEMM_ACT_DGELU) {
+    v *= dgelu_f(__bfloat162float(p.aux_in[row * p.ld_aux + col]));
+  } else if (p.act == GEMM_ACT_DRELU) {
+    v = __bfloat162float(p.aux_in[row * p.ld_aux + col]) > 0.0f ? v : 0.0f;
+  }
+  if (p.residual) v += __bfloat162float(p.residual[row * p.ldr + col]);
+  if (p.c_fp32) {
+    float* c = (float*)c_base + row * p.ldc + col;
+    if (p.accumulate) v += *c;
+    *c = v;
+  } else {
+    __nv_bfloat16* c = (__nv_bfloat16*)c_base + row * p.ldc + col;
+    if (p.accumulate) v += __bfloat162float(*c);
+    *c = __float2bfloat16(v);
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows x 128 B.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;  // [2]
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_base_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_holder + 1);
+
+  const int warp_idx = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 128);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp_idx == 1) {
+    tmem_alloc(smem_u32(tmem_base_holder), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_holder;
+
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch_total;
+
+  auto tile_skipped = [&](int m0, int n0) -> bool {
+    if (p.causal_tiles == 1) return n0 > m0 + BM - 1;
+    if (p.causal_tiles == 2) return m0 > n0 + BN - 1;
+    return false;
+  };
+
+  if (warp_idx == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int b = tile / tiles_per_batch;
+        const int t = tile - b * tiles_per_batch;
+        const int m0 = (t % p.tiles_m) * BM;
+        const int n0 = (t / p.tiles_m) * BN;
+        if (tile_skipped(m0, n0)) continue;
+        const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag,
+                                 &g_gemm_error, 1)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+          const uint32_t sb = smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_4d(sa, &tmap_a, fb, k0, m0, bi, bo);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_4d(sa + c * (64 * BK * 2), &tmap_a, fb, m0 + 64 * c, k0, bi, bo);
+          }
+          if (!p.b_mn) {
+            tma_load_4d(sb, &tmap_b, fb, k0, n0, bi, bo);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_4d(sb + c * (64 * BK * 2), &tmap_b, fb, n0 + 64 * c, k0, bi, bo);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Give loads already in flight time to land before the CTA releases its
+        // shared memory.
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp_idx == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      // K-major: 8-row groups 1024 B apart, k-step of 16 elements = 32 B inside the span.
+      // MN-major: 64-element chunks 64*BK*2 B apart (LBO), 8-k groups 1024 B apart (SBO),
+      //           k-step of 16 = two groups = 2048 B.
+      const uint32_t a_lbo = p.a_mn ? 64 * BK * 2 : 16, b_lbo = p.b_mn ? 64 * BK * 2 : 16;
+      const uint32_t a_step = p.a_mn ? (2048 >> 4) : (32 >> 4);
+      const uint32_t b_step = p.b_mn ? (2048 >> 4) : (32 >> 4);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int b = tile / tiles_per_batch;
+        const int t = tile - b * tiles_per_batch;
+        const int m0 = (t % p.tiles_m) * BM;
+        const int n0 = (t / p.tiles_m) * BN;
+        if (tile_skipped(m0, n0)) continue;
+        if (!mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag,
+                               &g_gemm_error, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag, &g_gemm_error,
+                                 3)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t a_desc = make_smem_desc_sw128(
+              smem_u32(smem_a + stage * A_STAGE_BYTES), a_lbo, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(
+              smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES), b_lbo, 1024);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            umma_bf16(d_tmem, a_desc + (uint64_t)(j * a_step), b_desc + (uint64_t)(j * b_step),
+                      idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));  // frees the smem stage when MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&tmem_full_bar[acc]));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quad = warp_idx & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int b = tile / tiles_per_batch;
+      const int t = tile - b * tiles_per_batch;
+      const int m0 = (t % p.tiles_m) * BM;
+      const int n0 = (t / p.tiles_m) * BN;
+      if (tile_skipped(m0, n0)) continue;
+      const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+      if (!mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, &g_gemm_error,
+                             4)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const long long row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const size_t esz = p.c_fp32 ? 4 : 2;
+      char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = n0 + c0;
+        if (col0 >= p.N) break;  // uniform across the CTA
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        if (p.vec_ok && col0 + 32 <= p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (p.bias) {
+            if (p.bias_fp32) {
+              const float4* bp = reinterpret_cast<const float4*>((const float*)p.bias + col0);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 bv = __ldg(bp + i);
+                v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
+              }
+            } else {
+              const uint4* bp =
+                  reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.bias + col0);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float f[8];
+                unpack8(__ldg(bp + i), f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
+              }
+            }
+          }
+          if (p.act == GEMM_ACT_GELU || p.act == GEMM_ACT_RELU) {
+            if (p.aux_out) {
+              uint4* ap = reinterpret_cast<uint4*>(p.aux_out + row * p.ldc + col0);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) ap[i] = pack8(v + 8 * i);
+            }
+            if (p.act == GEMM_ACT_GELU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+            }
+          } else if (p.act == GEMM_ACT_DGELU || p.act == GEMM_ACT_DRELU) {
+            const uint4* xp = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux + col0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float f[8];
+              unpack8(__ldg(xp + i), f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (p.act == GEMM_ACT_DGELU) v[8 * i + j] *= dgelu_f(f[j]);
+                else v[8 * i + j] = f[j] > 0.0f ? v[8 * i + j] : 0.0f;
+              }
+            }
+          }
+          if (p.residual) {
+            const uint4* rp = reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float f[8];
+              unpack8(__ldg(rp + i), f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
+            }
+          }
+          if (p.c_fp32) {
+            float4* cp = reinterpret_cast<float4*>((float*)c_base + row * p.ldc + col0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              if (p.accumulate) {
+                float4 old = cp[i];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              cp[i] = o;
+            }
+          } else {
+            uint4* cp = reinterpret_cast<uint4*>((__nv_bfloat16*)c_base + row * p.ldc + col0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (p.accumulate) {
+                float f[8];
+                unpack8(cp[i], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
+              }
+              cp[i] = pack8(v + 8 * i);
+            }
+          }
+        } else {
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            if (col < p.N) epilogue_store_scalar(p, c_base, row, col, __uint_as_float(r[i]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp_idx == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------
+// SIMT fallback: any stride / alignment, same epilogue. Only meant for the small or
+// misaligned shapes TMA cannot address (e.g. a [256, 10] classifier head).
+// ------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ B,
+                 long long a_sm, long long a_sk, long long b_sk, long long b_sn,
+                 long long a_stride_inner, long long a_stride_outer, long long b_stride_inner,
+                 long long b_stride_outer, KernelParams p) {
+  constexpr int T = 32, KT = 32;
+  __shared__ float sa[KT][T + 1];
+  __shared__ float sb[KT][T + 1];
+  const int b = blockIdx.z;
+  const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+  A += bi * a_stride_inner + bo * a_stride_outer;
+  B += bi * b_stride_inner + bo * b_stride_outer;
+  const size_t esz = p.c_fp32 ? 4 : 2;
+  char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
+  const int m0 = blockIdx.y * T, n0 = blockIdx.x * T;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 2x2 outputs each
+  float acc[2][2] = {{0, 0}, {0, 0}};
+  for (int k0 = 0; k0 < p.K; k0 += KT) {
+    for (int i = threadIdx.x; i < T * KT; i += 256) {
+      int kk, mm;
+      if (a_sk == 1) { kk = i % KT; mm = i / KT; } else { mm = i % T; kk = i / T; }
+      int m = m0 + mm, k = k0 + kk;
+      sa[kk][mm] = (m < p.M && k < p.K) ? __bfloat162float(A[m * a_sm + k * a_sk]) : 0.0f;
+      int nn;
+      if (b_sk == 1) { kk = i % KT; nn = i / KT; } else { nn = i % T; kk = i / T; }
+      int n = n0 + nn;
+      k = k0 + kk;
+      sb[kk][nn] = (n < p.N && k < p.K) ? __bfloat162float(B[k * b_sk + n * b_sn]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < KT; ++kk) {
+      float a0 = sa[kk][ty], a1 = sa[kk][ty + 16];
+      float b0 = sb[kk][tx], b1 = sb[kk][tx + 16];
+      acc[0][0] += a0 * b0; acc[0][1] += a0 * b1;
+      acc[1][0] += a1 * b0; acc[1][1] += a1 * b1;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      int m = m0 + ty + 16 * i, n = n0 + tx + 16 * j;
+      if (m < p.M && n < p.N) epilogue_store_scalar(p, c_base, m, n, acc[i][j]);
+    }
+}
+
+// ------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault,
+                                         &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 4-D bf16 tensor map: (inner, rows, batch_inner, batch_outer), 128-byte swizzle.
+bool encode_operand_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows,
+                        uint64_t nbi, uint64_t nbo, int64_t ld, int64_t stride_bi,
+                        int64_t stride_bo, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  if (stride_bi <= 0) stride_bi = ld * (int64_t)rows;
+  if (stride_bo <= 0) stride_bo = stride_bi * (int64_t)nbi;
+  cuuint64_t dims[4] = {inner, rows, nbi, nbo};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)stride_bi * 2,
+                           (cuuint64_t)stride_bo * 2};
+  cuuint32_t box[4] = {box_inner, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+std::atomic<uint64_t> g_launches{0};
+
+int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+KernelParams make_params(const GemmArgs& a) {
+  KernelParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.tiles_m = 0; p.tiles_n = 0;
+  p.batch_inner = a.batch_inner < 1 ? 1 : a.batch_inner;
+  p.batch_total = p.batch_inner * (a.batch_outer < 1 ? 1 : a.batch_outer);
+  p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
+  p.C = a.C; p.ldc = a.ldc;
+  p.c_stride_inner = a.c_stride_inner; p.c_stride_outer = a.c_stride_outer;
+  p.alpha = a.alpha; p.c_fp32 = a.c_fp32; p.accumulate = a.accumulate;
+  p.bias = a.bias; p.bias_fp32 = a.bias_fp32; p.act = a.act;
+  p.residual = (const __nv_bfloat16*)a.residual; p.ldr = a.ldr;
+  p.aux_out = (__nv_bfloat16*)a.aux_out;
+  p.aux_in = (const __nv_bfloat16*)a.aux_in; p.ld_aux = a.ld_aux;
+  p.causal_tiles = a.causal_tiles;
+  const int cvec = a.c_fp32 ? 4 : 8;
+  bool v = aligned16(a.C) && (a.ldc % cvec == 0) && (a.c_stride_inner % cvec == 0) &&
+           (a.c_stride_outer % cvec == 0);
+  if (a.bias) v = v && aligned16(a.bias);
+  if (a.residual) v = v && aligned16(a.residual) && (a.ldr % 8 == 0);
+  if (a.aux_out) v = v && aligned16(a.aux_out) && (a.ldc % 8 == 0);
+  if (a.aux_in) v = v && aligned16(a.aux_in) && (a.ld_aux % 8 == 0);
+  p.vec_ok = v ? 1 : 0;
+  return p;
+}
+
+template <int BN>
+cudaError_t launch_tc(const GemmArgs& a, cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  KernelParams p = make_params(a);
+  p.tiles_m = (a.M + BM - 1) / BM;
+  p.tiles_n = (a.N + BN - 1) / BN;
+  CUtensorMap ta, tb;
+  const uint64_t nbi = p.batch_inner, nbo = p.batch_total / p.batch_inner;
+  bool ok;
+  if (!a.a_mn_major)
+    ok = encode_operand_map(&ta, a.A, a.K, a.M, nbi, nbo, a.lda, a.a_stride_inner,
+                            a.a_stride_outer, BK, BM);
+  else
+    ok = encode_operand_map(&ta, a.A, a.M, a.K, nbi, nbo, a.lda, a.a_stride_inner,
+                            a.a_stride_outer, 64, BK);
+  if (!a.b_mn_major)
+    ok = ok && encode_operand_map(&tb, a.B, a.K, a.N, nbi, nbo, a.ldb, a.b_stride_inner,
+                                  a.b_stride_outer, BK, BN);
+  else
+    ok = ok && encode_operand_map(&tb, a.B, a.N, a.K, nbi, nbo, a.ldb, a.b_stride_inner,
+                                  a.b_stride_outer, 64, BK);
+  if (!ok) return cudaErrorInvalidValue;
+  const long long total = (long long)p.tiles_m * p.tiles_n * p.batch_total;
+  const int grid = (int)(total < num_sms() ? total : num_sms());
+  gemm_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_simt(const GemmArgs& a, cudaStream_t stream) {
+  KernelParams p = make_params(a);
+  p.vec_ok = 0;
+  long long a_sm = a.a_mn_major ? 1 : a.lda, a_sk = a.a_mn_major ? a.lda : 1;
+  long long b_sk = a.b_mn_major ? a.ldb : 1, b_sn = a.b_mn_major ? 1 : a.ldb;
+  dim3 grid((a.N + 31) / 32, (a.M + 31) / 32, p.batch_total);
+  gemm_simt_kernel<<<grid, 256, 0, stream>>>(
+      (const __nv_bfloat16*)a.A, (const __nv_bfloat16*)a.B, a_sm, a_sk, b_sk, b_sn,
+      a.a_stride_inner, a.a_stride_outer, a.b_stride_inner, a.b_stride_outer, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_uses_tensor_cores(const GemmArgs& a) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) return false;
+  if (!aligned16(a.A) || !aligned16(a.B)) return false;
+  if (a.lda % 8 || a.ldb % 8) return false;
+  if (a.a_stride_inner % 8 || a.a_stride_outer % 8 || a.b_stride_inner % 8 ||
+      a.b_stride_outer % 8)
+    return false;
+  // Tiny problems are not worth a 128-row tile.
+  if ((long long)a.M * a.N < 64 * 64 && a.batch_inner * a.batch_outer == 1) return false;
+  if (a.N < 16) return false;
+  return true;
+}
+
+cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return cudaSuccess;
+  if (a.K <= 0) return cudaErrorInvalidValue;
+  if (!gemm_uses_tensor_cores(a)) return launch_simt(a, stream);
+  // Tile width: prefer 256-wide tiles when they fill the machine, otherwise 128.
+  const long long batch = (long long)(a.batch_inner < 1 ? 1 : a.batch_inner) *
+                          (a.batch_outer < 1 ? 1 : a.batch_outer);
+  const long long tm = (a.M + BM - 1) / BM;
+  const long long t256 = tm * ((a.N + 255) / 256) * batch;
+  const long long t128 = tm * ((a.N + 127) / 128) * batch;
+  const int sms = num_sms();
+  auto eff = [&](long long tiles) {
+    long long waves = (tiles + sms - 1) / sms;
+    return (double)tiles / (double)(waves * sms);
+  };
+  // Wider tiles reuse each A tile twice as much; take them unless the narrower tile
+  // wins clearly on wave quantisation.
+  const bool use256 = a.N > 128 && eff(t256) + 0.10 >= eff(t128);
+  if (use256) return launch_tc<256>(a, stream);
+  return launch_tc<128>(a, stream);
+}
+
+int gemm_last_device_error() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
+  return v;
+}
+void gemm_clear_device_error() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_gemm_error, &v, sizeof(int));
+}
+uint64_t gemm_launch_count() { return g_launches.load(); }
+
+}  // namespace lt
