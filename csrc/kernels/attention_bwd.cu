@@ -1,0 +1,477 @@
+// Flash attention backward on tcgen05 (no counterpart in the reference, which has no
+// attention backward at all: lua/luatorch/nn/flash_attention.lua:52-108 never records one).
+//
+// Three launches, no floating-point atomics, bitwise reproducible:
+//   1. delta[b,h,i] = sum_d dO[i,d] * O[i,d]
+//   2. dK/dV kernel: one CTA per 128-key tile, loops over the query tiles that see it.
+//        S = Q K^T and dP = dO V^T go to TMEM; thread r (query row r) rebuilds
+//        P = exp(scale*S - lse) and dS = P * (dP - delta) * scale and stores both as bf16 in
+//        the swizzled shared-memory layout; then dV += P^T dO and dK += dS^T Q accumulate in
+//        TMEM (the transposes are free: the same shared-memory bytes are described to the
+//        tensor core as an MN-major operand).
+//   3. dQ kernel: one CTA per 128-query tile, loops over its key tiles, recomputes S / dP,
+//        dQ += dS K accumulates in TMEM.
+#include "attention.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda.h>
+#include <atomic>
+
+namespace lt {
+
+using namespace ptx;
+
+extern std::atomic<uint64_t> g_attn_launches;
+extern __device__ int g_attn_error;
+
+namespace attn_detail {
+bool make_qkv_map(CUtensorMap* map, const void* base, int D, int S, int H, int B, int64_t ss,
+                  int64_t sh, int64_t sb, int box_rows);
+}
+
+namespace {
+
+constexpr int BT = 128;                  // tile edge (queries and keys)
+constexpr int CHUNK_BYTES = 128 * 128;   // 128 rows x 64 bf16
+constexpr int NUM_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct BwdParams {
+  int S, H, causal;
+  float scale, scale_log2;
+  const float* lse;
+  const float* delta;
+  __nv_bfloat16* out0;  // dK (kernel 2) or dQ (kernel 3)
+  long long o0_sb, o0_ss, o0_sh;
+  __nv_bfloat16* out1;  // dV (kernel 2)
+  long long o1_sb, o1_ss, o1_sh;
+};
+
+// ------------------------------------------------------------------ delta = rowsum(dO * O)
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                  float* __restrict__ delta, int B, int H, int S, int D, long long o_sb,
+                  long long o_ss, long long o_sh, long long do_sb, long long do_ss,
+                  long long do_sh) {
+  const int lane = threadIdx.x & 31;
+  const long long r = blockIdx.x * 8ll + (threadIdx.x >> 5);  // over B*H*S
+  if (r >= (long long)B * H * S) return;
+  const int s = r % S, h = (r / S) % H, b = r / ((long long)S * H);
+  const __nv_bfloat16* op = o + b * o_sb + s * o_ss + h * o_sh;
+  const __nv_bfloat16* dp = d_o + b * do_sb + s * do_ss + h * do_sh;
+  float acc = 0.0f;
+  for (int i = lane * 2; i < D; i += 64) {
+    float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + i));
+    float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + i));
+    acc += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[r] = acc;
+}
+
+// Rebuild P and dS for one query row from the S / dP accumulators in TMEM and store them
+// (bf16) into the swizzled [query row][key] shared-memory tiles.
+template <bool WRITE_P>
+__device__ __forceinline__ void rebuild_row(uint32_t tmem_s, uint32_t tmem_dp, uint32_t lane_base,
+                                            int row, int valid, float lse_l2, float delta,
+                                            float c, float scale, uint8_t* p_tile,
+                                            uint8_t* ds_tile) {
+  const int row_off = (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll 1
+  for (int c32 = 0; c32 < 4; ++c32) {
+    uint32_t s[32], dp[32];
+    tmem_ld_32x32(tmem_s + lane_base + c32 * 32, s);
+    tmem_ld_32x32(tmem_dp + lane_base + c32 * 32, dp);
+    tmem_ld_wait();
+    uint32_t pp[16], dd[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = (c32 * 32 + i < valid) ? ex2(__uint_as_float(s[i]) * c - lse_l2) : 0.0f;
+      float p1 = (c32 * 32 + i + 1 < valid) ? ex2(__uint_as_float(s[i + 1]) * c - lse_l2) : 0.0f;
+      float d0 = p0 * (__uint_as_float(dp[i]) - delta) * scale;
+      float d1 = p1 * (__uint_as_float(dp[i + 1]) - delta) * scale;
+      __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+      pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
+      dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
+    }
+    const int chunk_off = (c32 >> 1) * CHUNK_BYTES + row_off;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int chunk16 = (((c32 & 1) * 4 + t) ^ (row & 7)) * 16;
+      if (WRITE_P)
+        *reinterpret_cast<uint4*>(p_tile + chunk_off + chunk16) =
+            make_uint4(pp[4 * t], pp[4 * t + 1], pp[4 * t + 2], pp[4 * t + 3]);
+      *reinterpret_cast<uint4*>(ds_tile + chunk_off + chunk16) =
+          make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
+    }
+  }
+}
+
+// Store one accumulator row (D fp32 columns in TMEM) as bf16.
+template <int D>
+__device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst) {
+#pragma unroll
+  for (int c32 = 0; c32 < D / 32; ++c32) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c32 * 32, r);
+    tmem_ld_wait();
+    if (dst) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 u;
+        __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          hb[t] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * t]),
+                                        __uint_as_float(r[i + 2 * t + 1]));
+        *reinterpret_cast<uint4*>(dst + c32 * 32 + i) = u;
+      }
+    }
+  }
+}
+
+template <int D, bool DKDV>
+struct BwdSmem {
+  static constexpr int DC = D / 64;
+  static constexpr int TILE = DC * CHUNK_BYTES;          // one [128 x D] operand
+  static constexpr int STAGES = D == 64 ? 2 : 1;         // streamed operand pair ring depth
+  static constexpr int OFF_FIX0 = 0;                     // stationary operand 0 (K or Q)
+  static constexpr int OFF_FIX1 = TILE;                  // stationary operand 1 (V or dO)
+  static constexpr int OFF_STR = 2 * TILE;               // streamed pairs: [stage][2][TILE]
+  static constexpr int OFF_P = OFF_STR + STAGES * 2 * TILE;
+  static constexpr int OFF_DS = OFF_P + (DKDV ? 2 * CHUNK_BYTES : 0);
+  static constexpr int OFF_BAR = OFF_DS + 2 * CHUNK_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+// DKDV = true : stationary (K_j, V_j), streamed (Q_i, dO_i), outputs dK_j, dV_j
+// DKDV = false: stationary (Q_i, dO_i), streamed (K_j, V_j), output dQ_i
+template <int D, bool DKDV>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                 const BwdParams p) {
+  using L = BwdSmem<D, DKDV>;
+  constexpr int DC = L::DC, ST = L::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* fix_full = bars;        // 1
+  uint64_t* str_full = bars + 1;    // ST
+  uint64_t* str_empty = bars + 3;   // ST
+  uint64_t* s_full = bars + 5;      // 1  (S and dP ready in TMEM)
+  uint64_t* s_empty = bars + 6;     // 1  (compute warps done reading S / dP)
+  uint64_t* pds_full = bars + 7;    // 1  (P / dS tiles written)
+  uint64_t* pds_empty = bars + 8;   // 1  (MMAs reading P / dS retired)
+  uint64_t* acc_full = bars + 9;    // 1  (final accumulators ready)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_tiles = (p.S + BT - 1) / BT;
+  // DKDV: this CTA owns key tile `own`, streams query tiles [first, n_tiles)
+  // dQ  : this CTA owns query tile `own`, streams key tiles [0, last]
+  const int own = DKDV ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int it_begin = DKDV ? (p.causal ? own : 0) : 0;
+  const int it_end = DKDV ? n_tiles : (p.causal ? own + 1 : n_tiles);
+  const int n_it = it_end - it_begin;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(smem_u32(fix_full), 1);
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(smem_u32(&str_full[i]), 1);
+      mbar_init(smem_u32(&str_empty[i]), 1);
+    }
+    mbar_init(smem_u32(s_full), 1);
+    mbar_init(smem_u32(s_empty), 128);
+    mbar_init(smem_u32(pds_full), 128);
+    mbar_init(smem_u32(pds_empty), 1);
+    mbar_init(smem_u32(acc_full), 1);
+    fence_mbar_init();
+  }
+  if (warp_idx == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128;
+  const uint32_t tmem_acc0 = tmem_base + 256;        // dK or dQ
+  const uint32_t tmem_acc1 = tmem_base + 256 + D;    // dV
+
+  // shared-memory operand tiles; in both kernels "A-side" = the query-indexed pair (Q, dO)
+  // and "B-side" = the key-indexed pair (K, V)
+  auto fix0 = [&]() { return smem + L::OFF_FIX0; };
+  auto fix1 = [&]() { return smem + L::OFF_FIX1; };
+  auto str0 = [&](int st) { return smem + L::OFF_STR + st * 2 * L::TILE; };
+  auto str1 = [&](int st) { return smem + L::OFF_STR + st * 2 * L::TILE + L::TILE; };
+
+  if (warp_idx == 0) {
+    if (lane == 0) {
+      const uint32_t fb = smem_u32(fix_full);
+      mbar_arrive_expect_tx(fb, 2 * L::TILE);
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        tma_load_4d(smem_u32(fix0() + c * CHUNK_BYTES), DKDV ? &tm_k : &tm_q, fb, 64 * c, own * BT,
+                    h, b);
+        tma_load_4d(smem_u32(fix1() + c * CHUNK_BYTES), DKDV ? &tm_v : &tm_do, fb, 64 * c,
+                    own * BT, h, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % ST, use = it / ST, t = it_begin + it;
+        if (!mbar_wait_bounded(smem_u32(&str_empty[st]), (use & 1) ^ 1, abort_flag, &g_attn_error,
+                               31))
+          break;
+        const uint32_t sb = smem_u32(&str_full[st]);
+        mbar_arrive_expect_tx(sb, 2 * L::TILE);
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          tma_load_4d(smem_u32(str0(st) + c * CHUNK_BYTES), DKDV ? &tm_q : &tm_k, sb, 64 * c,
+                      t * BT, h, b);
+          tma_load_4d(smem_u32(str1(st) + c * CHUNK_BYTES), DKDV ? &tm_do : &tm_v, sb, 64 * c,
+                      t * BT, h, b);
+        }
+      }
+    }
+  } else if (warp_idx == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BT, BT, 0, 0);
+      const uint32_t idesc_kv = make_idesc_bf16(BT, D, 1, 1);  // P^T dO, dS^T Q
+      const uint32_t idesc_q = make_idesc_bf16(BT, D, 0, 1);   // dS K
+      bool ok = mbar_wait_bounded(smem_u32(fix_full), 0, abort_flag, &g_attn_error, 32);
+      // S = Q K^T and dP = dO V^T for iteration `it`
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it % ST, use = it / ST;
+        if (!mbar_wait_bounded(smem_u32(&str_full[st]), use & 1, abort_flag, &g_attn_error, 33))
+          return false;
+        if (!mbar_wait_bounded(smem_u32(s_empty), (it & 1) ^ 1, abort_flag, &g_attn_error, 34))
+          return false;
+        tc_fence_after_sync();
+        uint8_t* q_t = DKDV ? str0(st) : fix0();
+        uint8_t* do_t = DKDV ? str1(st) : fix1();
+        uint8_t* k_t = DKDV ? fix0() : str0(st);
+        uint8_t* v_t = DKDV ? fix1() : str1(st);
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          const uint64_t qd = make_smem_desc_sw128(smem_u32(q_t + c * CHUNK_BYTES), 16, 1024);
+          const uint64_t kd = make_smem_desc_sw128(smem_u32(k_t + c * CHUNK_BYTES), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(tmem_s, qd + (uint64_t)(ks * 2), kd + (uint64_t)(ks * 2), idesc_s,
+                      (c > 0 || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          const uint64_t dd = make_smem_desc_sw128(smem_u32(do_t + c * CHUNK_BYTES), 16, 1024);
+          const uint64_t vd = make_smem_desc_sw128(smem_u32(v_t + c * CHUNK_BYTES), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(tmem_dp, dd + (uint64_t)(ks * 2), vd + (uint64_t)(ks * 2), idesc_s,
+                      (c > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(s_full));
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_scores(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % ST;
+        if (!mbar_wait_bounded(smem_u32(pds_full), it & 1, abort_flag, &g_attn_error, 35)) {
+          ok = false;
+          break;
+        }
+        // with a 2-deep ring the next tile's scores go first so the compute warps restart
+        // while the accumulating MMAs below run
+        if (ST == 2 && it + 1 < n_it) {
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
+        tc_fence_after_sync();
+        uint8_t* p_t = smem + L::OFF_P;
+        uint8_t* ds_t = smem + L::OFF_DS;
+        if (DKDV) {
+          uint8_t* q_t = str0(st);
+          uint8_t* do_t = str1(st);
+          // dV[keys x D] += P^T dO ; dK[keys x D] += dS^T Q.  K dimension = 128 queries:
+          // rows of the P / dS / dO / Q tiles, 16 queries = 2048 B per step.
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t pd =
+                make_smem_desc_sw128(smem_u32(p_t) + ks * 2048, CHUNK_BYTES, 1024);
+            const uint64_t od =
+                make_smem_desc_sw128(smem_u32(do_t) + ks * 2048, CHUNK_BYTES, 1024);
+            umma_bf16(tmem_acc1, pd, od, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t sd =
+                make_smem_desc_sw128(smem_u32(ds_t) + ks * 2048, CHUNK_BYTES, 1024);
+            const uint64_t qd =
+                make_smem_desc_sw128(smem_u32(q_t) + ks * 2048, CHUNK_BYTES, 1024);
+            umma_bf16(tmem_acc0, sd, qd, idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+          }
+        } else {
+          uint8_t* k_t = str0(st);
+          // dQ[queries x D] += dS[queries x keys] K[keys x D]; K dimension = 128 keys
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc) {
+            const uint64_t sd =
+                make_smem_desc_sw128(smem_u32(ds_t + kc * CHUNK_BYTES), 16, 1024);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint64_t kd = make_smem_desc_sw128(
+                  smem_u32(k_t) + (kc * 64 + ks * 16) * 128, CHUNK_BYTES, 1024);
+              umma_bf16(tmem_acc0, sd + (uint64_t)(ks * 2), kd, idesc_q,
+                        (it > 0 || kc > 0 || ks > 0) ? 1u : 0u);
+            }
+          }
+        }
+        umma_commit(smem_u32(pds_empty));
+        umma_commit(smem_u32(&str_empty[st]));
+        if (ST == 1 && it + 1 < n_it) {
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
+      }
+      if (ok) umma_commit(smem_u32(acc_full));
+    }
+  } else {
+    const int quad = warp_idx & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    bool ok = true;
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int t = it_begin + it;
+      const int q_tile = DKDV ? t : own, k_tile = DKDV ? own : t;
+      const int qi = q_tile * BT + row, k0 = k_tile * BT;
+      int valid = 0;
+      float lse_l2 = 0.0f, delta = 0.0f;
+      if (qi < p.S) {
+        int lim = p.S - k0;
+        if (p.causal) { int cl = qi - k0 + 1; lim = cl < lim ? cl : lim; }
+        valid = lim < 0 ? 0 : (lim > BT ? BT : lim);
+        const long long idx = ((long long)b * p.H + h) * p.S + qi;
+        lse_l2 = p.lse[idx] * LOG2E;
+        delta = p.delta[idx];
+      }
+      if (!mbar_wait_bounded(smem_u32(s_full), it & 1, abort_flag, &g_attn_error, 36) ||
+          !mbar_wait_bounded(smem_u32(pds_empty), (it & 1) ^ 1, abort_flag, &g_attn_error, 37)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      rebuild_row<DKDV>(tmem_s, tmem_dp, lane_base, row, valid, lse_l2, delta, p.scale_log2,
+                        p.scale, smem + L::OFF_P, smem + L::OFF_DS);
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(s_empty));
+      fence_proxy_async();
+      mbar_arrive(smem_u32(pds_full));
+    }
+    if (ok && n_it > 0 &&
+        mbar_wait_bounded(smem_u32(acc_full), 0, abort_flag, &g_attn_error, 38)) {
+      tc_fence_after_sync();
+      const int gi = own * BT + row;  // key index (DKDV) or query index
+      const bool in_range = gi < p.S;
+      __nv_bfloat16* d0 = in_range ? p.out0 + (long long)b * p.o0_sb + (long long)gi * p.o0_ss +
+                                         (long long)h * p.o0_sh
+                                   : nullptr;
+      store_acc_row<D>(tmem_acc0 + lane_base, d0);
+      if (DKDV) {
+        __nv_bfloat16* d1 = in_range ? p.out1 + (long long)b * p.o1_sb + (long long)gi * p.o1_ss +
+                                           (long long)h * p.o1_sh
+                                     : nullptr;
+        store_acc_row<D>(tmem_acc1 + lane_base, d1);
+      }
+    } else if (ok && n_it == 0) {
+      // a key tile no query attends to (cannot happen for causal self-attention): zero output
+      const int gi = own * BT + row;
+      if (gi < p.S) {
+        __nv_bfloat16* d0 = p.out0 + (long long)b * p.o0_sb + (long long)gi * p.o0_ss +
+                            (long long)h * p.o0_sh;
+        for (int i = 0; i < D; ++i) d0[i] = __float2bfloat16(0.0f);
+        if (DKDV) {
+          __nv_bfloat16* d1 = p.out1 + (long long)b * p.o1_sb + (long long)gi * p.o1_ss +
+                              (long long)h * p.o1_sh;
+          for (int i = 0; i < D; ++i) d1[i] = __float2bfloat16(0.0f);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp_idx == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, bool DKDV>
+cudaError_t launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                       const CUtensorMap& tdo, const BwdParams& p, dim3 grid, cudaStream_t s) {
+  using L = BwdSmem<D, DKDV>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd_kernel<D, DKDV>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  flash_bwd_kernel<D, DKDV><<<grid, NUM_THREADS, L::TOTAL, s>>>(tq, tk, tv, tdo, p);
+  g_attn_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+bool ok8(int64_t a, int64_t b, int64_t c) { return a % 8 == 0 && b % 8 == 0 && c % 8 == 0; }
+
+}  // namespace
+
+cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cudaStream_t stream) {
+  if (a.B <= 0 || a.H <= 0 || a.S <= 0) return cudaSuccess;
+  if (a.D != 64 && a.D != 128) return cudaErrorInvalidValue;
+  if (!ok8(a.q_ss, a.q_sh, a.q_sb) || !ok8(a.k_ss, a.k_sh, a.k_sb) || !ok8(a.v_ss, a.v_sh, a.v_sb) ||
+      !ok8(g.do_ss, g.do_sh, g.do_sb) || !ok8(g.dq_ss, g.dq_sh, g.dq_sb) ||
+      !ok8(g.dk_ss, g.dk_sh, g.dk_sb) || !ok8(g.dv_ss, g.dv_sh, g.dv_sb))
+    return cudaErrorInvalidValue;
+
+  const long long rows = (long long)a.B * a.H * a.S;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+      (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)g.d_o, g.delta, a.B, a.H, a.S, a.D, a.o_sb,
+      a.o_ss, a.o_sh, g.do_sb, g.do_ss, g.do_sh);
+  g_attn_launches.fetch_add(1, std::memory_order_relaxed);
+
+  CUtensorMap tq, tk, tv, tdo;
+  if (!attn_detail::make_qkv_map(&tq, a.q, a.D, a.S, a.H, a.B, a.q_ss, a.q_sh, a.q_sb, BT) ||
+      !attn_detail::make_qkv_map(&tk, a.k, a.D, a.S, a.H, a.B, a.k_ss, a.k_sh, a.k_sb, BT) ||
+      !attn_detail::make_qkv_map(&tv, a.v, a.D, a.S, a.H, a.B, a.v_ss, a.v_sh, a.v_sb, BT) ||
+      !attn_detail::make_qkv_map(&tdo, g.d_o, a.D, a.S, a.H, a.B, g.do_ss, g.do_sh, g.do_sb, BT))
+    return cudaErrorInvalidValue;
+
+  BwdParams p;
+  p.S = a.S; p.H = a.H; p.causal = a.causal;
+  p.scale = a.scale; p.scale_log2 = a.scale * LOG2E;
+  p.lse = a.lse; p.delta = g.delta;
+  dim3 grid((a.S + BT - 1) / BT, a.H, a.B);
+
+  p.out0 = (__nv_bfloat16*)g.dk; p.o0_sb = g.dk_sb; p.o0_ss = g.dk_ss; p.o0_sh = g.dk_sh;
+  p.out1 = (__nv_bfloat16*)g.dv; p.o1_sb = g.dv_sb; p.o1_ss = g.dv_ss; p.o1_sh = g.dv_sh;
+  cudaError_t e = a.D == 64 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, grid, stream)
+                            : launch_bwd<128, true>(tq, tk, tv, tdo, p, grid, stream);
+  if (e != cudaSuccess) return e;
+
+  p.out0 = (__nv_bfloat16*)g.dq; p.o0_sb = g.dq_sb; p.o0_ss = g.dq_ss; p.o0_sh = g.dq_sh;
+  p.out1 = nullptr; p.o1_sb = p.o1_ss = p.o1_sh = 0;
+  return a.D == 64 ? launch_bwd<64, false>(tq, tk, tv, tdo, p, grid, stream)
+                   : launch_bwd<128, false>(tq, tk, tv, tdo, p, grid, stream);
+}
+
+}  // namespace lt

@@ -1,0 +1,431 @@
+// Causal / non-causal flash attention forward on tcgen05.
+//
+// One CTA per (128-query tile, head, batch); 192 threads:
+//   warp 0      TMA producer: Q once, then K/V tiles through a 2-stage ring
+//   warp 1      MMA issuer: S = Q K^T into one of two TMEM score buffers, O_tile = P V
+//   warps 2..5  softmax: thread r owns query row r; reads S from TMEM, keeps the running
+//               max / sum and the output row in registers, writes P (bf16) into shared
+//               memory in the 128-byte-swizzled layout the tensor core expects as operand A
+// S for tile j+1 is issued before P V of tile j, so the tensor core works while the softmax
+// warps are busy with exponentials.  Tiles above the causal diagonal are never loaded.
+#include "attention.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda.h>
+#include <atomic>
+#include <mutex>
+
+namespace lt {
+
+using namespace ptx;
+
+std::atomic<uint64_t> g_attn_launches{0};
+__device__ int g_attn_error = 0;
+
+int attention_last_device_error() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int));
+  return v;
+}
+uint64_t attention_launch_count() { return g_attn_launches.load(); }
+
+namespace attn_detail {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault,
+                                         &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// (head_dim, seq, head, batch) bf16 map with a (64, rows, 1, 1) box and 128-byte swizzle.
+bool make_qkv_map(CUtensorMap* map, const void* base, int D, int S, int H, int B, int64_t ss,
+                  int64_t sh, int64_t sb, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace attn_detail
+
+namespace {
+
+constexpr int BM = 128;       // queries per CTA
+constexpr int BN = 128;       // keys per tile
+constexpr int CHUNK_BYTES = 128 * 128;  // 128 rows x 64 bf16, one swizzled operand chunk
+constexpr int NUM_THREADS = 192;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct FwdParams {
+  int S, H;
+  int causal;
+  float scale_log2;  // scale * log2(e)
+  float scale;
+  __nv_bfloat16* o;
+  long long o_sb, o_ss, o_sh;
+  float* lse;
+};
+
+template <int D>
+struct FwdSmem {
+  static constexpr int DC = D / 64;                 // 64-wide head_dim chunks
+  static constexpr int Q_BYTES = DC * CHUNK_BYTES;
+  static constexpr int KV_BYTES = DC * CHUNK_BYTES;
+  static constexpr int P_BYTES = 2 * CHUNK_BYTES;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;          // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;     // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using L = FwdSmem<D>;
+  constexpr int DC = L::DC;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // 2
+  uint64_t* v_full = bars + 3;        // 2
+  uint64_t* kv_empty = bars + 5;      // 2
+  uint64_t* s_full = bars + 7;        // 2
+  uint64_t* s_empty = bars + 9;       // 2
+  uint64_t* p_full = bars + 11;       // 1
+  uint64_t* o_full = bars + 12;       // 1
+  uint64_t* o_empty = bars + 13;      // 1
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // longest (most key tiles) query tiles first
+  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * BM;
+  const int n_kv_all = (p.S + BN - 1) / BN;
+  const int n_kv = p.causal ? (q_tile + 1 < n_kv_all ? q_tile + 1 : n_kv_all) : n_kv_all;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(smem_u32(q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&k_full[i]), 1);
+      mbar_init(smem_u32(&v_full[i]), 1);
+      mbar_init(smem_u32(&kv_empty[i]), 1);
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&s_empty[i]), 128);
+    }
+    mbar_init(smem_u32(p_full), 128);
+    mbar_init(smem_u32(o_full), 1);
+    mbar_init(smem_u32(o_empty), 128);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp_idx == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;          // two score buffers: +0, +128
+  const uint32_t tmem_o = tmem_base + 256;    // D columns
+
+  if (warp_idx == 0) {
+    if (lane == 0) {
+      const uint32_t qb = smem_u32(q_full);
+      mbar_arrive_expect_tx(qb, L::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < DC; ++c)
+        tma_load_4d(smem_u32(smem + L::OFF_Q + c * CHUNK_BYTES), &tm_q, qb, 64 * c, q0, h, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait_bounded(smem_u32(&kv_empty[st]), ((j >> 1) & 1) ^ 1, abort_flag,
+                               &g_attn_error, 11))
+          break;
+        const uint32_t kb = smem_u32(&k_full[st]), vb = smem_u32(&v_full[st]);
+        mbar_arrive_expect_tx(kb, L::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < DC; ++c)
+          tma_load_4d(smem_u32(smem + L::OFF_K + st * L::KV_BYTES + c * CHUNK_BYTES), &tm_k, kb,
+                      64 * c, j * BN, h, b);
+        mbar_arrive_expect_tx(vb, L::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < DC; ++c)
+          tma_load_4d(smem_u32(smem + L::OFF_V + st * L::KV_BYTES + c * CHUNK_BYTES), &tm_v, vb,
+                      64 * c, j * BN, h, b);
+      }
+    }
+  } else if (warp_idx == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(BM, D, 0, 1);
+      bool ok = mbar_wait_bounded(smem_u32(q_full), 0, abort_flag, &g_attn_error, 12);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait_bounded(smem_u32(&k_full[st]), (j >> 1) & 1, abort_flag, &g_attn_error, 13))
+          return false;
+        if (!mbar_wait_bounded(smem_u32(&s_empty[st]), ((j >> 1) & 1) ^ 1, abort_flag,
+                               &g_attn_error, 14))
+          return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          const uint64_t qd =
+              make_smem_desc_sw128(smem_u32(smem + L::OFF_Q + c * CHUNK_BYTES), 16, 1024);
+          const uint64_t kd = make_smem_desc_sw128(
+              smem_u32(smem + L::OFF_K + st * L::KV_BYTES + c * CHUNK_BYTES), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(tmem_s + st * BN, qd + (uint64_t)(ks * 2), kd + (uint64_t)(ks * 2), idesc_s,
+                      (c > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_full[st]));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_kv) {
+          if (!issue_s(j + 1)) { ok = false; break; }
+        }
+        if (!mbar_wait_bounded(smem_u32(&v_full[st]), (j >> 1) & 1, abort_flag, &g_attn_error, 15) ||
+            !mbar_wait_bounded(smem_u32(p_full), j & 1, abort_flag, &g_attn_error, 16) ||
+            !mbar_wait_bounded(smem_u32(o_empty), (j & 1) ^ 1, abort_flag, &g_attn_error, 17)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // O_tile[128 x D] = P[128 x 128 keys] * V[128 keys x D]; keys are the K dimension:
+        // two 64-key chunks of P, V rows 8-key groups 1024 B apart, 16 keys = 2048 B per step.
+#pragma unroll
+        for (int kc = 0; kc < 2; ++kc) {
+          const uint64_t pd =
+              make_smem_desc_sw128(smem_u32(smem + L::OFF_P + kc * CHUNK_BYTES), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * L::KV_BYTES) +
+                                    (kc * 64 + ks * 16) * 128;
+            const uint64_t vd = make_smem_desc_sw128(v_addr, CHUNK_BYTES, 1024);
+            umma_bf16(tmem_o, pd + (uint64_t)(ks * 2), vd, idesc_o, (kc > 0 || ks > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(o_full));
+        umma_commit(smem_u32(&kv_empty[st]));
+      }
+    }
+  } else {
+    // ------------------------------ softmax / output ------------------------------
+    const int quad = warp_idx & 3;
+    const int row = quad * 32 + lane;      // query row inside the tile
+    const int qi = q0 + row;               // global query index
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    float m = -INFINITY, l = 0.0f;
+    float o_acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_acc[i] = 0.0f;
+    const float c = p.scale_log2;
+    bool ok = true;
+    uint8_t* p_row = smem + L::OFF_P + (row >> 3) * 1024 + (row & 7) * 128;
+
+    for (int j = 0; ok && j < n_kv; ++j) {
+      const int st = j & 1;
+      if (!mbar_wait_bounded(smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag, &g_attn_error, 18)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int k0 = j * BN;
+      const bool need_mask = (p.causal && k0 + BN - 1 > q0) || (k0 + BN > p.S);
+      // number of valid key columns for this row inside the tile
+      int valid = BN;
+      if (need_mask) {
+        int lim = p.S - k0;
+        if (p.causal) { int cl = qi - k0 + 1; lim = cl < lim ? cl : lim; }
+        valid = lim < 0 ? 0 : (lim > BN ? BN : lim);
+      }
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c32 = 0; c32 < 4; ++c32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_base + st * BN + c32 * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float sv = __uint_as_float(r[i]);
+          if (c32 * 32 + i < valid) mx = fmaxf(mx, sv);
+        }
+      }
+      const float m_new = mx;
+      const float alpha = (m == -INFINITY) ? 0.0f : ex2((m - m_new) * c);
+      // fold in the previous tile's P V product, then rescale to the new maximum
+      if (j > 0) {
+        if (!mbar_wait_bounded(smem_u32(o_full), (j - 1) & 1, abort_flag, &g_attn_error, 19)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c32 = 0; c32 < D / 32; ++c32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_base + c32 * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c32 * 32 + i] += __uint_as_float(r[i]);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(o_empty));
+      }
+#pragma unroll
+      for (int i = 0; i < D; ++i) o_acc[i] *= alpha;
+      l *= alpha;
+      // pass 2: exponentials -> P (bf16, swizzled operand-A layout) + row sum
+      const float mc = (m_new == -INFINITY) ? 0.0f : m_new * c;
+      float rsum = 0.0f;
+#pragma unroll 1
+      for (int c32 = 0; c32 < 4; ++c32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_base + st * BN + c32 * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = (c32 * 32 + i < valid) ? ex2(__uint_as_float(r[i]) * c - mc) : 0.0f;
+          float p1 = (c32 * 32 + i + 1 < valid) ? ex2(__uint_as_float(r[i + 1]) * c - mc) : 0.0f;
+          rsum += p0 + p1;
+          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
+        }
+        uint8_t* dst = p_row + (c32 >> 1) * CHUNK_BYTES;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int chunk16 = ((c32 & 1) * 4 + t) ^ (row & 7);
+          *reinterpret_cast<uint4*>(dst + chunk16 * 16) =
+              make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+        }
+      }
+      l += rsum;
+      m = m_new;
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&s_empty[st]));
+      fence_proxy_async();
+      mbar_arrive(smem_u32(p_full));
+    }
+    if (ok && n_kv > 0) {
+      if (mbar_wait_bounded(smem_u32(o_full), (n_kv - 1) & 1, abort_flag, &g_attn_error, 20)) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c32 = 0; c32 < D / 32; ++c32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_base + c32 * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c32 * 32 + i] += __uint_as_float(r[i]);
+        }
+        if (qi < p.S) {
+          const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+          __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_ss +
+                                (long long)h * p.o_sh;
+#pragma unroll
+          for (int i = 0; i < D; i += 8) {
+            uint4 u;
+            __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              hb[t] = __floats2bfloat162_rn(o_acc[i + 2 * t] * inv, o_acc[i + 2 * t + 1] * inv);
+            *reinterpret_cast<uint4*>(orow + i) = u;
+          }
+          if (p.lse)
+            p.lse[((long long)b * p.H + h) * p.S + qi] =
+                (l > 0.0f) ? m * p.scale + __logf(l) : -INFINITY;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp_idx == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t stream) {
+  using L = FwdSmem<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  CUtensorMap tq, tk, tv;
+  if (!attn_detail::make_qkv_map(&tq, a.q, a.D, a.S, a.H, a.B, a.q_ss, a.q_sh, a.q_sb, BM) ||
+      !attn_detail::make_qkv_map(&tk, a.k, a.D, a.S, a.H, a.B, a.k_ss, a.k_sh, a.k_sb, BN) ||
+      !attn_detail::make_qkv_map(&tv, a.v, a.D, a.S, a.H, a.B, a.v_ss, a.v_sh, a.v_sb, BN))
+    return cudaErrorInvalidValue;
+  FwdParams p;
+  p.S = a.S; p.H = a.H; p.causal = a.causal;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.o = (__nv_bfloat16*)a.o;
+  p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
+  p.lse = a.lse;
+  dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
+  flash_fwd_kernel<D><<<grid, NUM_THREADS, L::TOTAL, stream>>>(tq, tk, tv, p);
+  g_attn_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+bool strides_ok(int64_t ss, int64_t sh, int64_t sb) {
+  return ss % 8 == 0 && sh % 8 == 0 && sb % 8 == 0;
+}
+
+}  // namespace
+
+cudaError_t flash_attention_forward(const AttnArgs& a, cudaStream_t stream) {
+  if (a.B <= 0 || a.H <= 0 || a.S <= 0) return cudaSuccess;
+  if (a.D != 64 && a.D != 128) return cudaErrorInvalidValue;
+  if (!strides_ok(a.q_ss, a.q_sh, a.q_sb) || !strides_ok(a.k_ss, a.k_sh, a.k_sb) ||
+      !strides_ok(a.v_ss, a.v_sh, a.v_sb) || !strides_ok(a.o_ss, a.o_sh, a.o_sb))
+    return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
+       reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.o)) & 15)
+    return cudaErrorInvalidValue;
+  return a.D == 64 ? launch_fwd<64>(a, stream) : launch_fwd<128>(a, stream);
+}
+
+}  // namespace lt

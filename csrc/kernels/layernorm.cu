@@ -1,0 +1,428 @@
+// LayerNorm forward / backward and GELU+bias forward / backward.
+//
+// Forward: one warp per row, the row is read ONCE into registers (16-byte vectors), mean
+// and variance are reduced with warp shuffles, mean / rstd are saved for backward.  The
+// reference kernel reads each row three times from global memory and has no backward at
+// all (csrc/cuda/ops/fused.cu:63-127); its Lua LayerNorm backward walks elements on the
+// CPU (lua/luatorch/nn/layernorm.lua:76-126).
+// Backward: one warp per row computes dx (optionally adding an incoming residual gradient)
+// while accumulating dgamma / dbeta partials in registers; partials are folded per block in
+// shared memory, written to scratch, and a second kernel reduces them in a fixed order.
+#include "ops.h"
+#include "common.cuh"
+
+namespace lt {
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int BWD_MAX_BLOCKS = 296;  // two CTAs per SM on a 148-SM part
+
+template <typename TP> __device__ __forceinline__ float ldp(const TP* p, int64_t i) {
+  return VecIO<TP>::ld(p + i);
+}
+
+// ----------------------------------------------------------------------------- forward
+// NV = 16-byte vectors per lane (row length <= 32 * NV * V elements).
+template <typename T, typename TP, int NV>
+__global__ void __launch_bounds__(THREADS)
+ln_fwd_kernel(const T* __restrict__ x, const TP* __restrict__ gamma, const TP* __restrict__ beta,
+              float eps, T* __restrict__ y, float* __restrict__ mean_out,
+              float* __restrict__ rstd_out, int64_t rows, int64_t cols) {
+  constexpr int V = VecIO<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * (int64_t)WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t nvec = cols / V;
+  const T* xr = x + row * cols;
+  float v[NV][V];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int64_t vi = lane + 32 * i;
+    if (vi < nvec) {
+      VecIO<T>::load(xr + vi * V, v[i]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) sum += v[i][j];
+    }
+  }
+  const float mean = warp_sum(sum) / (float)cols;
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) { float d = v[i][j] - mean; sq += d * d; }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / (float)cols + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * cols;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int64_t vi = lane + 32 * i;
+    if (vi < nvec) {
+      float o[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        o[j] = (v[i][j] - mean) * rstd * ldp(gamma, vi * V + j) + ldp(beta, vi * V + j);
+      VecIO<T>::store(yr + vi * V, o);
+    }
+  }
+}
+
+// Any row length / alignment: one CTA per row, scalar accesses.
+template <typename T, typename TP>
+__global__ void __launch_bounds__(THREADS)
+ln_fwd_generic(const T* __restrict__ x, const TP* __restrict__ gamma, const TP* __restrict__ beta,
+               float eps, T* __restrict__ y, float* __restrict__ mean_out,
+               float* __restrict__ rstd_out, int64_t cols) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * cols;
+  float s = 0.0f;
+  for (int64_t c = threadIdx.x; c < cols; c += THREADS) s += VecIO<T>::ld(xr + c);
+  const float mean = block_sum(s, sh) / (float)cols;
+  float q = 0.0f;
+  for (int64_t c = threadIdx.x; c < cols; c += THREADS) {
+    float d = VecIO<T>::ld(xr + c) - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(q, sh) / (float)cols + eps);
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  for (int64_t c = threadIdx.x; c < cols; c += THREADS)
+    VecIO<T>::st(y + row * cols + c,
+                 (VecIO<T>::ld(xr + c) - mean) * rstd * ldp(gamma, c) + ldp(beta, c));
+}
+
+// ----------------------------------------------------------------------------- backward
+template <typename T, typename TP, int NV>
+__global__ void __launch_bounds__(THREADS)
+ln_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
+              const float* __restrict__ mean, const float* __restrict__ rstd,
+              const T* __restrict__ dx_add, T* __restrict__ dx, float* __restrict__ scratch,
+              int64_t rows, int64_t cols) {
+  constexpr int V = VecIO<T>::N;
+  extern __shared__ float sh_acc[];  // [2][cols]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t nvec = cols / V;
+  float dg[NV][V], db[NV][V], gm[NV][V];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int64_t vi = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      dg[i][j] = 0.0f; db[i][j] = 0.0f;
+      gm[i][j] = vi < nvec ? ldp(gamma, vi * V + j) : 0.0f;
+    }
+  }
+  for (int64_t row = blockIdx.x * (int64_t)WARPS + warp; row < rows;
+       row += (int64_t)gridDim.x * WARPS) {
+    const T* xr = x + row * cols;
+    const T* dyr = dy + row * cols;
+    const float mu = mean[row], rs = rstd[row];
+    float c1 = 0.0f, c2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t vi = lane + 32 * i;
+      if (vi < nvec) {
+        float xv[V], dv[V];
+        VecIO<T>::load(xr + vi * V, xv);
+        VecIO<T>::load(dyr + vi * V, dv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          const float g = dv[j] * gm[i][j];
+          c1 += g; c2 += g * xh;
+          dg[i][j] += dv[j] * xh;
+          db[i][j] += dv[j];
+        }
+      }
+    }
+    c1 = warp_sum(c1) / (float)cols;
+    c2 = warp_sum(c2) / (float)cols;
+    T* dxr = dx + row * cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t vi = lane + 32 * i;
+      if (vi < nvec) {
+        float xv[V], dv[V], o[V];
+        VecIO<T>::load(xr + vi * V, xv);   // second touch comes from L1 / L2
+        VecIO<T>::load(dyr + vi * V, dv);
+        if (dx_add) VecIO<T>::load(dx_add + row * cols + vi * V, o);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          const float r = rs * (dv[j] * gm[i][j] - c1 - xh * c2);
+          o[j] = dx_add ? o[j] + r : r;
+        }
+        VecIO<T>::store(dxr + vi * V, o);
+      }
+    }
+  }
+  // fold the eight warps of this block in a fixed order
+  for (int c = threadIdx.x; c < 2 * cols; c += THREADS) sh_acc[c] = 0.0f;
+  __syncthreads();
+  for (int w = 0; w < WARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int64_t vi = lane + 32 * i;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            sh_acc[vi * V + j] += dg[i][j];
+            sh_acc[cols + vi * V + j] += db[i][j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* out = scratch + (int64_t)blockIdx.x * 2 * cols;
+  for (int c = threadIdx.x; c < 2 * cols; c += THREADS) out[c] = sh_acc[c];
+}
+
+template <typename T, typename TP>
+__global__ void __launch_bounds__(THREADS)
+ln_bwd_generic(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
+               const float* __restrict__ mean, const float* __restrict__ rstd,
+               const T* __restrict__ dx_add, T* __restrict__ dx, int64_t cols) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.x;
+  const float mu = mean[row], rs = rstd[row];
+  float c1 = 0.0f, c2 = 0.0f;
+  for (int64_t c = threadIdx.x; c < cols; c += THREADS) {
+    const float xh = (VecIO<T>::ld(x + row * cols + c) - mu) * rs;
+    const float g = VecIO<T>::ld(dy + row * cols + c) * ldp(gamma, c);
+    c1 += g; c2 += g * xh;
+  }
+  c1 = block_sum(c1, sh) / (float)cols;
+  c2 = block_sum(c2, sh) / (float)cols;
+  for (int64_t c = threadIdx.x; c < cols; c += THREADS) {
+    const float xh = (VecIO<T>::ld(x + row * cols + c) - mu) * rs;
+    const float g = VecIO<T>::ld(dy + row * cols + c) * ldp(gamma, c);
+    float r = rs * (g - c1 - xh * c2);
+    if (dx_add) r += VecIO<T>::ld(dx_add + row * cols + c);
+    VecIO<T>::st(dx + row * cols + c, r);
+  }
+}
+
+// dgamma / dbeta partials for the generic path: slab sums over 128 rows, thread per column.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ln_param_partials_generic(const T* __restrict__ x, const T* __restrict__ dy,
+                          const float* __restrict__ mean, const float* __restrict__ rstd,
+                          float* __restrict__ scratch, int64_t rows, int64_t cols,
+                          int64_t rows_per_slab) {
+  const int64_t c = blockIdx.x * 256ll + threadIdx.x;
+  if (c >= cols) return;
+  const int64_t r0 = blockIdx.y * rows_per_slab;
+  const int64_t r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+  float g = 0.0f, b = 0.0f;
+  for (int64_t r = r0; r < r1; ++r) {
+    const float d = VecIO<T>::ld(dy + r * cols + c);
+    g += d * (VecIO<T>::ld(x + r * cols + c) - mean[r]) * rstd[r];
+    b += d;
+  }
+  scratch[(int64_t)blockIdx.y * 2 * cols + c] = g;
+  scratch[(int64_t)blockIdx.y * 2 * cols + cols + c] = b;
+}
+
+template <typename TG>
+__global__ void ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
+                                TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate) {
+  const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (c >= 2 * cols) return;
+  float t = 0.0f;
+  for (int p = 0; p < nparts; ++p) t += scratch[(int64_t)p * 2 * cols + c];
+  TG* dst = c < cols ? dgamma + c : dbeta + (c - cols);
+  if (accumulate) t += VecIO<TG>::ld(dst);
+  VecIO<TG>::st(dst, t);
+}
+
+int bwd_blocks(int64_t rows) {
+  int64_t need = (rows + WARPS - 1) / WARPS;
+  return (int)(need < BWD_MAX_BLOCKS ? (need < 1 ? 1 : need) : BWD_MAX_BLOCKS);
+}
+
+template <typename T, typename TP>
+cudaError_t ln_fwd_dispatch(const void* x, const void* gamma, const void* beta, float eps, void* y,
+                            float* mean, float* rstd, int64_t rows, int64_t cols,
+                            cudaStream_t s) {
+  constexpr int V = VecIO<T>::N;
+  const bool fast = cols % V == 0 && cols <= 32 * 8 * V && is_aligned16(x) && is_aligned16(y);
+  const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
+#define LT_LN_FWD(NVV)                                                                       \
+  ln_fwd_kernel<T, TP, NVV><<<grid, THREADS, 0, s>>>((const T*)x, (const TP*)gamma,          \
+                                                     (const TP*)beta, eps, (T*)y, mean, rstd, \
+                                                     rows, cols)
+  if (fast) {
+    const int64_t per_lane = (cols / V + 31) / 32;
+    if (per_lane <= 1) LT_LN_FWD(1);
+    else if (per_lane <= 2) LT_LN_FWD(2);
+    else if (per_lane <= 3) LT_LN_FWD(3);
+    else if (per_lane <= 4) LT_LN_FWD(4);
+    else LT_LN_FWD(8);
+  } else {
+    ln_fwd_generic<T, TP><<<(unsigned)rows, THREADS, 0, s>>>(
+        (const T*)x, (const TP*)gamma, (const TP*)beta, eps, (T*)y, mean, rstd, cols);
+  }
+#undef LT_LN_FWD
+  LT_COUNT_LAUNCH();
+  return cudaGetLastError();
+}
+
+template <typename T, typename TP>
+cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, const float* mean,
+                            const float* rstd, const void* dx_add, void* dx, float* scratch,
+                            int64_t rows, int64_t cols, int* nparts, cudaStream_t s) {
+  constexpr int V = VecIO<T>::N;
+  const bool fast = cols % V == 0 && cols <= 32 * 8 * V && is_aligned16(x) && is_aligned16(dy) &&
+                    is_aligned16(dx) && (!dx_add || is_aligned16(dx_add));
+  if (fast) {
+    const int grid = bwd_blocks(rows);
+    *nparts = grid;
+    const size_t smem = 2 * cols * sizeof(float);
+#define LT_LN_BWD(NVV)                                                                    \
+  ln_bwd_kernel<T, TP, NVV><<<grid, THREADS, smem, s>>>(                                   \
+      (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx,   \
+      scratch, rows, cols)
+    const int64_t per_lane = (cols / V + 31) / 32;
+    if (per_lane <= 1) LT_LN_BWD(1);
+    else if (per_lane <= 2) LT_LN_BWD(2);
+    else if (per_lane <= 3) LT_LN_BWD(3);
+    else if (per_lane <= 4) LT_LN_BWD(4);
+    else LT_LN_BWD(8);
+#undef LT_LN_BWD
+    LT_COUNT_LAUNCH();
+  } else {
+    ln_bwd_generic<T, TP><<<(unsigned)rows, THREADS, 0, s>>>(
+        (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx, cols);
+    LT_COUNT_LAUNCH();
+    const int slabs = bwd_blocks(rows);
+    const int64_t rps = (rows + slabs - 1) / slabs;
+    *nparts = slabs;
+    dim3 g((unsigned)((cols + 255) / 256), (unsigned)slabs);
+    ln_param_partials_generic<T><<<g, 256, 0, s>>>((const T*)x, (const T*)dy, mean, rstd, scratch,
+                                                   rows, cols, rps);
+    LT_COUNT_LAUNCH();
+  }
+  return cudaGetLastError();
+}
+
+// ----------------------------------------------------------------------------- gelu + bias
+template <typename T, typename TP, bool BWD>
+__global__ void __launch_bounds__(256)
+gelu_bias_kernel(const T* __restrict__ x, const TP* __restrict__ bias, const T* __restrict__ dy,
+                 T* __restrict__ out, int64_t rows, int64_t cols, int vec_ok) {
+  constexpr int V = VecIO<T>::N;
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    const int64_t cv = cols / V, nvec = rows * cv;
+    for (int64_t i = tid; i < nvec; i += nthreads) {
+      const int64_t c = (i % cv) * V;
+      float xv[V], dv[V];
+      VecIO<T>::load(x + i * V, xv);
+      if (BWD) VecIO<T>::load(dy + i * V, dv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float z = xv[j] + (bias ? ldp(bias, c + j) : 0.0f);
+        xv[j] = BWD ? dv[j] * dgelu_exact_tanh(z) : gelu_exact_tanh(z);
+      }
+      VecIO<T>::store(out + i * V, xv);
+    }
+  } else {
+    const int64_t n = rows * cols;
+    for (int64_t i = tid; i < n; i += nthreads) {
+      const float z = VecIO<T>::ld(x + i) + (bias ? ldp(bias, i % cols) : 0.0f);
+      VecIO<T>::st(out + i, BWD ? VecIO<T>::ld(dy + i) * dgelu_exact_tanh(z) : gelu_exact_tanh(z));
+    }
+  }
+}
+
+template <typename T, typename TP, bool BWD>
+cudaError_t gelu_bias_launch(const void* x, const void* bias, const void* dy, void* out,
+                             int64_t rows, int64_t cols, cudaStream_t s) {
+  if (rows * cols <= 0) return cudaSuccess;
+  const int vec_ok = cols % VecIO<T>::N == 0 && is_aligned16(x) && is_aligned16(out) &&
+                     (!BWD || is_aligned16(dy));
+  gelu_bias_kernel<T, TP, BWD><<<stream_grid(rows * cols / VecIO<T>::N + 1, 256), 256, 0, s>>>(
+      (const T*)x, (const TP*)bias, (const T*)dy, (T*)out, rows, cols, vec_ok);
+  LT_COUNT_LAUNCH();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t layernorm_forward(int dtype, const void* x, const void* gamma, const void* beta,
+                              int param_dtype, float eps, void* y, float* mean, float* rstd,
+                              int64_t rows, int64_t cols, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  LT_DISPATCH_DTYPE(dtype, T, {
+    LT_DISPATCH_DTYPE(param_dtype, TP, {
+      return ln_fwd_dispatch<T, TP>(x, gamma, beta, eps, y, mean, rstd, rows, cols, s);
+    })
+  })
+  return cudaErrorInvalidValue;
+}
+
+int64_t layernorm_backward_scratch_floats(int64_t rows, int64_t cols) {
+  (void)rows;
+  return (int64_t)BWD_MAX_BLOCKS * 2 * cols;
+}
+
+cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const void* gamma,
+                               int param_dtype, const float* mean, const float* rstd,
+                               const void* dx_add, void* dx, void* dgamma, void* dbeta,
+                               int grad_dtype, int accumulate, float* scratch, int64_t rows,
+                               int64_t cols, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  int nparts = 0;
+  cudaError_t e = cudaErrorInvalidValue;
+  LT_DISPATCH_DTYPE(dtype, T, {
+    LT_DISPATCH_DTYPE(param_dtype, TP, {
+      e = ln_bwd_dispatch<T, TP>(x, dy, gamma, mean, rstd, dx_add, dx, scratch, rows, cols,
+                                 &nparts, s);
+    })
+  })
+  if (e != cudaSuccess) return e;
+  if (dgamma && dbeta) {
+    LT_DISPATCH_DTYPE(grad_dtype, TG, {
+      ln_param_reduce<TG><<<(unsigned)((2 * cols + 255) / 256), 256, 0, s>>>(
+          scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
+      LT_COUNT_LAUNCH();
+    })
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t gelu_bias_forward(int dtype, const void* x, const void* bias, int bias_dtype,
+                              void* out, int64_t rows, int64_t cols, cudaStream_t s) {
+  LT_DISPATCH_DTYPE(dtype, T, {
+    LT_DISPATCH_DTYPE(bias_dtype, TP, {
+      return gelu_bias_launch<T, TP, false>(x, bias, nullptr, out, rows, cols, s);
+    })
+  })
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t gelu_bias_backward(int dtype, const void* x, const void* bias, int bias_dtype,
+                               const void* dy, void* dx, int64_t rows, int64_t cols,
+                               cudaStream_t s) {
+  LT_DISPATCH_DTYPE(dtype, T, {
+    LT_DISPATCH_DTYPE(bias_dtype, TP, {
+      return gelu_bias_launch<T, TP, true>(x, bias, dy, dx, rows, cols, s);
+    })
+  })
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace lt
