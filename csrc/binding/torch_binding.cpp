@@ -156,6 +156,15 @@ Tensor add_broadcast(const Tensor& a, const Tensor& bias) {
                           a.size(1), cur_stream()), "add_broadcast");
   return out;
 }
+Tensor affine_cols(const Tensor& a, const Tensor& scale, const OptT& shift) {
+  need_cuda_contig(a, "a"); need_cuda_contig(scale, "scale");
+  TORCH_CHECK(a.dim() == 2 && scale.numel() == a.size(1) && scale.scalar_type() == a.scalar_type());
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = at::empty_like(a);
+  check(lt::affine_cols(dt(a), a.data_ptr(), scale.data_ptr(), optptr(shift), out.data_ptr(),
+                        a.size(0), a.size(1), cur_stream()), "affine_cols");
+  return out;
+}
 // out (optional, [cols], any float dtype) receives / accumulates the column sums of in[rows, cols]
 Tensor column_sum(const Tensor& in, const OptT& out_opt, bool accumulate) {
   TORCH_CHECK(in.is_cuda() && in.dim() == 2 && in.stride(1) == 1);
@@ -594,6 +603,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("unary", &unary);
   m.def("unary_backward", &unary_backward);
   m.def("add_broadcast", &add_broadcast);
+  m.def("affine_cols", &affine_cols);
   m.def("column_sum", &column_sum);
   m.def("cast", &cast);
   m.def("cast_into", &cast_into);

@@ -203,6 +203,35 @@ cudaError_t add_broadcast(int dtype, const void* a, const void* bias, void* out,
   return cudaErrorInvalidValue;
 }
 
+// out[r, c] = a[r, c] * scale[c] + shift[c]   (shift may be null)
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+affine_cols_kernel(const T* __restrict__ a, const T* __restrict__ scale,
+                   const T* __restrict__ shift, T* __restrict__ out, int64_t rows, int64_t cols) {
+  const int64_t n = rows * cols;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c = i % cols;
+    float v = VecIO<T>::ld(a + i) * VecIO<T>::ld(scale + c);
+    if (shift) v += VecIO<T>::ld(shift + c);
+    VecIO<T>::st(out + i, v);
+  }
+}
+}  // namespace
+
+cudaError_t affine_cols(int dtype, const void* a, const void* scale, const void* shift, void* out,
+                        int64_t rows, int64_t cols, cudaStream_t s) {
+  if (rows * cols <= 0) return cudaSuccess;
+  LT_DISPATCH_DTYPE(dtype, T, {
+    affine_cols_kernel<T><<<stream_grid(rows * cols, THREADS), THREADS, 0, s>>>(
+        (const T*)a, (const T*)scale, (const T*)shift, (T*)out, rows, cols);
+    LT_COUNT_LAUNCH();
+    return cudaGetLastError();
+  })
+  return cudaErrorInvalidValue;
+}
+
 // ------------------------------------------------------------------------------ column sum
 // Stage 1: each block sums a 128-row slab for 32*V... columns into scratch[slab, col] (fp32).
 // Stage 2: one thread per column adds the slabs in a fixed order => bitwise deterministic,

@@ -30,6 +30,9 @@ cudaError_t unary_backward(int op, int dtype, const void* x, const void* dy, voi
                            cudaStream_t s);
 cudaError_t add_broadcast(int dtype, const void* a, const void* bias, void* out, int64_t rows,
                           int64_t cols, cudaStream_t s);
+// out[r, c] = a[r, c] * scale[c] + shift[c] (shift may be null)
+cudaError_t affine_cols(int dtype, const void* a, const void* scale, const void* shift, void* out,
+                        int64_t rows, int64_t cols, cudaStream_t s);
 // out[c] = sum_r in[r, c]  (deterministic two-stage; `scratch` holds ceil(rows/128)*cols floats)
 cudaError_t column_sum(int dtype, const void* in, int64_t ld, void* out, int out_dtype,
                        int accumulate, int64_t rows, int64_t cols, float* scratch, cudaStream_t s);

@@ -341,7 +341,7 @@ def dropout_backward(dy: torch.Tensor, p: float, ctx) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------ matmul family
 def gemm(a, b, *, a_t=False, b_t=False, out=None, out_dtype=None, alpha=1.0, accumulate=False,
-         bias=None, act=0, residual=None, aux_out=None, aux_in=None, n_valid=None):
+         bias=None, act=0, residual=None, aux_out=None, aux_in=None, n_valid=None, k_valid=None):
     """C = act(alpha * op(a) @ op(b) + bias) + residual on the tensor cores (bf16 operands).
 
     a: [M, K] (or [K, M] when a_t), b: [K, N] (or [N, K] when b_t); both 2-d with unit inner
@@ -359,6 +359,8 @@ def gemm(a, b, *, a_t=False, b_t=False, out=None, out_dtype=None, alpha=1.0, acc
         N = b.shape[1]
     if n_valid is not None:
         N = n_valid
+    if k_valid is not None:
+        K = k_valid
     if out is None:
         out = torch.empty((M, N), device=a.device, dtype=out_dtype or torch.bfloat16)
     C.gemm(a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), bool(a_t), not b_t,
@@ -656,3 +658,102 @@ def launch_counts():
     """(gemm, memory-bound ops, attention, comm) kernel launches since import."""
     c = _load_ext()
     return tuple(c.launch_counts()) if c is not None else (0, 0, 0, 0)
+
+
+def affine_cols(a, scale, shift=None):
+    """a[r, c] * scale[c] (+ shift[c])."""
+    if a.is_cuda:
+        return ext().affine_cols(_k(a), _k(scale.to(a.dtype)),
+                                 None if shift is None else _k(shift.to(a.dtype)))
+    out = a * scale.reshape(1, -1)
+    return out if shift is None else out + shift.reshape(1, -1)
+
+
+# ------------------------------------------------------------------------------ attention (4-d)
+def _bgemm(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, H, Bn, a_s, b_s, c_s, alpha=1.0, causal=0):
+    ext().gemm(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, H, Bn, a_s[0], a_s[1], b_s[0], b_s[1],
+               c_s[0], c_s[1], alpha, False, None, 0, None, 0, None, None, 0, causal)
+
+
+def _attn_composed_forward(q, k, v, causal, scale):
+    """Attention for head sizes the flash kernel does not cover: batched tensor-core GEMMs
+    plus the score-softmax kernel, scores materialised as [B, H, S, S] bf16."""
+    Bn, S, H, D = q.shape
+    p = torch.empty((Bn, H, S, S), device=q.device, dtype=torch.bfloat16)
+    _bgemm(q, k, p, S, S, D, q.stride(1), k.stride(1), S, False, False, H, Bn,
+           (q.stride(2), q.stride(0)), (k.stride(2), k.stride(0)), (S * S, H * S * S), scale,
+           1 if causal else 0)
+    ext().softmax_scores(p, Bn * H, S, S, causal)
+    o = torch.empty((Bn, S, H, D), device=q.device, dtype=torch.bfloat16)
+    _bgemm(p, v, o, S, D, S, S, v.stride(1), H * D, False, True, H, Bn, (S * S, H * S * S),
+           (v.stride(2), v.stride(0)), (D, S * H * D))
+    return o, p
+
+
+def _attn_composed_backward(q, k, v, p, d_o, causal, scale, dq, dk, dv):
+    Bn, S, H, D = q.shape
+    ps = (S * S, H * S * S)
+    _bgemm(p, d_o, dv, S, D, S, S, d_o.stride(1), dv.stride(1), True, True, H, Bn, ps,
+           (d_o.stride(2), d_o.stride(0)), (dv.stride(2), dv.stride(0)))
+    dp = torch.empty_like(p)
+    _bgemm(d_o, v, dp, S, S, D, d_o.stride(1), v.stride(1), S, False, False, H, Bn,
+           (d_o.stride(2), d_o.stride(0)), (v.stride(2), v.stride(0)), ps, 1.0, 1 if causal else 0)
+    ext().softmax_scores_backward(p, dp, S, scale, causal)
+    _bgemm(dp, k, dq, S, D, S, S, k.stride(1), dq.stride(1), False, True, H, Bn, ps,
+           (k.stride(2), k.stride(0)), (dq.stride(2), dq.stride(0)))
+    _bgemm(dp, q, dk, S, D, S, S, q.stride(1), dk.stride(1), True, True, H, Bn, ps,
+           (q.stride(2), q.stride(0)), (dk.stride(2), dk.stride(0)))
+
+
+def attention_forward(q, k, v, causal: bool, scale: float):
+    """q, k, v: [B, S, H, D] views (unit stride on D). Returns (o [B, S, H, D], ctx)."""
+    D = q.shape[-1]
+    if q.is_cuda:
+        if q.dtype != torch.bfloat16:
+            q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+        if D in (64, 128):
+            o, lse = ext().flash_forward(q, k, v, causal, scale)
+            return o, ("flash", lse)
+        o, p = _attn_composed_forward(q, k, v, causal, scale)
+        return o, ("composed", p)
+    qh, kh, vh = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    s = torch.matmul(qh, kh.transpose(-1, -2)) * scale
+    if causal:
+        S = q.shape[1]
+        s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), -math.inf)
+    p = torch.softmax(s, -1)
+    o = torch.matmul(p, vh).permute(0, 2, 1, 3).contiguous().to(q.dtype)
+    return o, ("cpu", p)
+
+
+def attention_backward(q, k, v, o, ctx, d_o, causal: bool, scale: float, packed_out=None):
+    """Returns (dq, dk, dv) as [B, S, H, D]; with `packed_out` ([B, S, 3, H, D]) the three
+    gradients are written into it (the layout of a fused QKV activation)."""
+    kind, saved = ctx
+    if kind == "cpu":
+        p = saved
+        qh, kh, vh, doh = (t.float().permute(0, 2, 1, 3) for t in (q, k, v, d_o))
+        dv = torch.matmul(p.transpose(-1, -2), doh)
+        dp = torch.matmul(doh, vh.transpose(-1, -2))
+        ds = p * (dp - (dp * p).sum(-1, keepdim=True)) * scale
+        dq = torch.matmul(ds, kh)
+        dk = torch.matmul(ds.transpose(-1, -2), qh)
+        outs = [t.permute(0, 2, 1, 3).contiguous().to(q.dtype) for t in (dq, dk, dv)]
+        if packed_out is not None:
+            for i, t in enumerate(outs):
+                packed_out[:, :, i].copy_(t)
+        return outs
+    if q.dtype != torch.bfloat16:
+        q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    d_o = d_o if d_o.dtype == torch.bfloat16 else d_o.to(torch.bfloat16)
+    if d_o.stride(-1) != 1:
+        d_o = d_o.contiguous()
+    if kind == "flash":
+        return ext().flash_backward(q, k, v, o, saved, d_o, causal, scale, packed_out)
+    Bn, S, H, D = q.shape
+    if packed_out is not None:
+        dq, dk, dv = packed_out[:, :, 0], packed_out[:, :, 1], packed_out[:, :, 2]
+    else:
+        dq, dk, dv = (torch.empty((Bn, S, H, D), device=q.device, dtype=torch.bfloat16) for _ in range(3))
+    _attn_composed_backward(q, k, v, saved, d_o, causal, scale, dq, dk, dv)
+    return [dq, dk, dv]

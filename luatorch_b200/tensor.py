@@ -44,7 +44,8 @@ def _err(msg: str):
 class Tensor:
     """Dense tensor with the reference's object surface (`shape`, `ndim`, `dtype`, `device`)."""
 
-    __slots__ = ("_t", "requires_grad", "grad", "_node", "_grad_buf", "_compute", "_hook", "name")
+    __slots__ = ("_t", "requires_grad", "grad", "_node", "_grad_buf", "_compute", "_hook", "name",
+                 "_unit", "_base", "_base_slice")
 
     def __init__(self, shape=None, dtype: str = "float32", device: str = "cpu", _data=None):
         if _data is not None:
@@ -61,6 +62,9 @@ class Tensor:
         self._compute = None      # reduced-precision shadow used by kernels (bf16 copy of a master)
         self._hook = None         # called when the gradient of this tensor is final
         self.name = None
+        self._unit = False        # True for the all-ones seed gradient of backward()
+        self._base = None         # fused parameter this tensor is a column slice of
+        self._base_slice = None
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -187,7 +191,10 @@ class Tensor:
         if idx < 0 or idx >= n:
             _err(f"index {idx} out of bounds for tensor with {n} elements")
             return self
-        self._t.view(-1)[idx] = value
+        if self._t.is_contiguous():
+            self._t.view(-1)[idx] = value
+        else:
+            self._t[tuple(int(i) for i in torch.unravel_index(torch.tensor(idx), self._t.shape))] = value
         return self
 
     def reshape(self, shape: Sequence[int]) -> "Tensor":
@@ -209,7 +216,8 @@ class Tensor:
         return "Tensor(shape=%s, dtype=%s, device=%s)" % (
             "x".join(str(s) for s in self.shape), self.dtype, self.device)
 
-    __str__ = __repr__
+    def __str__(self) -> str:
+        return self.__repr__()
 
     # ------------------------------------------------------------------ operators
     def __add__(self, other):

@@ -1,0 +1,6 @@
+"""`lf.utils`: Logger and Config (lua/luatorch/init.lua:36-39) plus device timing helpers."""
+from .config import Config
+from .logger import Logger
+from .timing import ClockSampler, DeviceTimer
+
+__all__ = ["Logger", "Config", "DeviceTimer", "ClockSampler"]
