@@ -54,26 +54,30 @@ struct BwdParams {
 };
 
 // ------------------------------------------------------------------ delta = rowsum(dO * O)
+// One thread per (batch, position, head) row: D contiguous bf16 of O and dO, 16-byte loads;
+// neighbouring threads take neighbouring heads, which are adjacent in memory.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                   float* __restrict__ delta, int B, int H, int S, int D, long long o_sb,
                   long long o_ss, long long o_sh, long long do_sb, long long do_ss,
                   long long do_sh) {
-  const int lane = threadIdx.x & 31;
-  const long long r = blockIdx.x * 8ll + (threadIdx.x >> 5);  // over B*H*S
+  const long long r = blockIdx.x * 256ll + threadIdx.x;  // over B*S*H, head fastest
   if (r >= (long long)B * H * S) return;
-  const int s = r % S, h = (r / S) % H, b = r / ((long long)S * H);
-  const __nv_bfloat16* op = o + b * o_sb + s * o_ss + h * o_sh;
-  const __nv_bfloat16* dp = d_o + b * do_sb + s * do_ss + h * do_sh;
+  const int h = r % H, s = (r / H) % S, b = r / ((long long)S * H);
+  const uint4* op = reinterpret_cast<const uint4*>(o + b * o_sb + s * o_ss + h * o_sh);
+  const uint4* dp = reinterpret_cast<const uint4*>(d_o + b * do_sb + s * do_ss + h * do_sh);
   float acc = 0.0f;
-  for (int i = lane * 2; i < D; i += 64) {
-    float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + i));
-    float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + i));
-    acc += x.x * y.x + x.y * y.y;
-  }
+  for (int i = 0; i < D / 8; ++i) {
+    const uint4 x = op[i], y = dp[i];
+    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&x);
+    const __nv_bfloat162* yh = reinterpret_cast<const __nv_bfloat162*>(&y);
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) delta[r] = acc;
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = __bfloat1622float2(xh[j]), c = __bfloat1622float2(yh[j]);
+      acc += a.x * c.x + a.y * c.y;
+    }
+  }
+  delta[((long long)b * H + h) * S + s] = acc;
 }
 
 // Rebuild P and dS for one query row from the S / dP accumulators in TMEM and store them
@@ -444,7 +448,7 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
     return cudaErrorInvalidValue;
 
   const long long rows = (long long)a.B * a.H * a.S;
-  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+  attn_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, stream>>>(
       (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)g.d_o, g.delta, a.B, a.H, a.S, a.D, a.o_sb,
       a.o_ss, a.o_sh, g.do_sb, g.do_ss, g.do_sh);
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);

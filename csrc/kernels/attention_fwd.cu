@@ -99,18 +99,27 @@ struct FwdSmem {
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;     // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  // head_dim 64: one score buffer and 256 TMEM columns so that TWO CTAs share an SM (their
+  // softmax and MMA phases interleave); head_dim 128 fills the SM with one CTA and double
+  // buffers the scores instead.
+  static constexpr int NSB = D == 64 ? 1 : 2;
+  static constexpr int TMEM_COLS = D == 64 ? 256 : 512;
+  static constexpr int TOTAL = OFF_BAR + 256;   // base must be 1024-byte aligned (checked)
 };
 
 template <int D>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, (D == 64 ? 2 : 1))
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using L = FwdSmem<D>;
   constexpr int DC = L::DC;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
+  constexpr int NSB = L::NSB;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023) {  // swizzled operand tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(&g_attn_error, 0, 40);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // 2
@@ -151,15 +160,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tma_prefetch_desc(&tm_v);
   }
   if (warp_idx == 1) {
-    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_alloc(smem_u32(tmem_holder), L::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_s = tmem_base;          // two score buffers: +0, +128
-  const uint32_t tmem_o = tmem_base + 256;    // D columns
+  const uint32_t tmem_s = tmem_base;                // NSB score buffers of 128 columns
+  const uint32_t tmem_o = tmem_base + NSB * 128;    // D columns
 
   if (warp_idx == 0) {
     if (lane == 0) {
@@ -193,10 +202,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bool ok = mbar_wait_bounded(smem_u32(q_full), 0, abort_flag, &g_attn_error, 12);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
+        const int sb = NSB == 2 ? st : 0;                 // score buffer
+        const int su = NSB == 2 ? (j >> 1) : j;           // how often it has been used
         if (!mbar_wait_bounded(smem_u32(&k_full[st]), (j >> 1) & 1, abort_flag, &g_attn_error, 13))
           return false;
-        if (!mbar_wait_bounded(smem_u32(&s_empty[st]), ((j >> 1) & 1) ^ 1, abort_flag,
-                               &g_attn_error, 14))
+        if (!mbar_wait_bounded(smem_u32(&s_empty[sb]), (su & 1) ^ 1, abort_flag, &g_attn_error,
+                               14))
           return false;
         tc_fence_after_sync();
 #pragma unroll
@@ -207,16 +218,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               smem_u32(smem + L::OFF_K + st * L::KV_BYTES + c * CHUNK_BYTES), 16, 1024);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_bf16(tmem_s + st * BN, qd + (uint64_t)(ks * 2), kd + (uint64_t)(ks * 2), idesc_s,
+            umma_bf16(tmem_s + sb * BN, qd + (uint64_t)(ks * 2), kd + (uint64_t)(ks * 2), idesc_s,
                       (c > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(smem_u32(&s_full[st]));
+        umma_commit(smem_u32(&s_full[sb]));
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1;
-        if (j + 1 < n_kv) {
+        if (NSB == 2 && j + 1 < n_kv) {
           if (!issue_s(j + 1)) { ok = false; break; }
         }
         if (!mbar_wait_bounded(smem_u32(&v_full[st]), (j >> 1) & 1, abort_flag, &g_attn_error, 15) ||
@@ -242,6 +253,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         umma_commit(smem_u32(o_full));
         umma_commit(smem_u32(&kv_empty[st]));
+        if (NSB == 1 && j + 1 < n_kv) {
+          // single score buffer: the softmax warps released it just before p_full
+          if (!issue_s(j + 1)) { ok = false; break; }
+        }
       }
     }
   } else {
@@ -259,8 +274,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     uint8_t* p_row = smem + L::OFF_P + (row >> 3) * 1024 + (row & 7) * 128;
 
     for (int j = 0; ok && j < n_kv; ++j) {
-      const int st = j & 1;
-      if (!mbar_wait_bounded(smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag, &g_attn_error, 18)) {
+      const int st = NSB == 2 ? (j & 1) : 0;
+      const int su = NSB == 2 ? (j >> 1) : j;
+      if (!mbar_wait_bounded(smem_u32(&s_full[st]), su & 1, abort_flag, &g_attn_error, 18)) {
         ok = false;
         break;
       }
@@ -378,7 +394,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   if (warp_idx == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
   }
 }
 

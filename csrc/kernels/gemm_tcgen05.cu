@@ -31,7 +31,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quadrant, each half the columns
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
 template <int BN>
@@ -39,7 +40,7 @@ struct TileCfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;   // 4 at BN=256, 6 at BN=128
-  static constexpr int TMEM_COLS = 2 * BN >= 32 ? 2 * BN : 32;  // power of two for 64/128/256
+  static constexpr int TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);  // power of two
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -63,6 +64,7 @@ struct KernelParams {
   long long ld_aux;
   int causal_tiles;
   int vec_ok;  // C / residual / aux rows allow 16-byte vector access
+  int vec32_ok;  // ... and 32-byte (256-bit) access
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -130,6 +132,53 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return u;
 }
 
+// 32 consecutive bf16 (64 bytes) of one output row: two 256-bit accesses when the address is
+// 32-byte aligned (full sectors per instruction), else four 128-bit ones.
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v, int vec32) {
+  if (vec32) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 a = pack8(v + 16 * h), b = pack8(v + 16 * h + 8);
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * h),
+                   "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                   : "memory");
+    }
+  } else {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[i] = pack8(v + 8 * i);
+  }
+}
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float* v, int vec32) {
+  if (vec32) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4 a, b;
+      asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z),
+                     "=r"(b.w)
+                   : "l"(src + 16 * h)
+                   : "memory");
+      float f[8];
+      unpack8(a, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[16 * h + j] = f[j];
+      unpack8(b, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[16 * h + 8 + j] = f[j];
+    }
+  } else {
+    const uint4* sp = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+      unpack8(sp[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[8 * i + j] = f[j];
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -161,7 +210,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 128);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 32 * EPI_WARPS);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
@@ -288,6 +337,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // -------------------------------- epilogue --------------------------------
     const int quad = warp_idx & 3;  // TMEM lane quadrant this warp may read
+    const int half = (warp_idx - 2) >> 2;         // which half of the tile's columns
+    constexpr int HALF_COLS = BN / 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -310,9 +361,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
         const int col0 = n0 + c0;
-        if (col0 >= p.N) break;  // uniform across the CTA
+        if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
@@ -320,7 +371,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (p.vec_ok && col0 + 32 <= p.N) {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+          }
           if (p.bias) {
             if (p.bias_fp32) {
               const float4* bp = reinterpret_cast<const float4*>((const float*)p.bias + col0);
@@ -343,9 +398,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (p.act == GEMM_ACT_GELU || p.act == GEMM_ACT_RELU) {
             if (p.aux_out) {
-              uint4* ap = reinterpret_cast<uint4*>(p.aux_out + row * p.ldc + col0);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) ap[i] = pack8(v + 8 * i);
+              store_bf16x32(p.aux_out + row * p.ldc + col0, v, p.vec32_ok);
             }
             if (p.act == GEMM_ACT_GELU) {
 #pragma unroll
@@ -355,27 +408,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
             }
           } else if (p.act == GEMM_ACT_DGELU || p.act == GEMM_ACT_DRELU) {
-            const uint4* xp = reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux + col0);
+            float x[32];
+            load_bf16x32(p.aux_in + row * p.ld_aux + col0, x, p.vec32_ok);
+            if (p.act == GEMM_ACT_DGELU) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float f[8];
-              unpack8(__ldg(xp + i), f);
+              for (int i = 0; i < 32; ++i) v[i] *= dgelu_f(x[i]);
+            } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (p.act == GEMM_ACT_DGELU) v[8 * i + j] *= dgelu_f(f[j]);
-                else v[8 * i + j] = f[j] > 0.0f ? v[8 * i + j] : 0.0f;
-              }
+              for (int i = 0; i < 32; ++i) v[i] = x[i] > 0.0f ? v[i] : 0.0f;
             }
           }
           if (p.residual) {
-            const uint4* rp = reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col0);
+            float x[32];
+            load_bf16x32(p.residual + row * p.ldr + col0, x, p.vec32_ok);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float f[8];
-              unpack8(__ldg(rp + i), f);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
-            }
+            for (int i = 0; i < 32; ++i) v[i] += x[i];
           }
           if (p.c_fp32) {
             float4* cp = reinterpret_cast<float4*>((float*)c_base + row * p.ldc + col0);
@@ -389,17 +436,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               cp[i] = o;
             }
           } else {
-            uint4* cp = reinterpret_cast<uint4*>((__nv_bfloat16*)c_base + row * p.ldc + col0);
+            __nv_bfloat16* cp = (__nv_bfloat16*)c_base + row * p.ldc + col0;
+            if (p.accumulate) {
+              float x[32];
+              load_bf16x32(cp, x, p.vec32_ok);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (p.accumulate) {
-                float f[8];
-                unpack8(cp[i], f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
-              }
-              cp[i] = pack8(v + 8 * i);
+              for (int i = 0; i < 32; ++i) v[i] += x[i];
             }
+            store_bf16x32(cp, v, p.vec32_ok);
           }
         } else {
           for (int i = 0; i < 32; ++i) {
@@ -553,6 +597,13 @@ KernelParams make_params(const GemmArgs& a) {
   if (a.aux_out) v = v && aligned16(a.aux_out) && (a.ldc % 8 == 0);
   if (a.aux_in) v = v && aligned16(a.aux_in) && (a.ld_aux % 8 == 0);
   p.vec_ok = v ? 1 : 0;
+  auto a32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+  bool w = v && !a.c_fp32 && a32(a.C) && a.ldc % 16 == 0 && a.c_stride_inner % 16 == 0 &&
+           a.c_stride_outer % 16 == 0;
+  if (a.residual) w = w && a32(a.residual) && a.ldr % 16 == 0;
+  if (a.aux_out) w = w && a32(a.aux_out);
+  if (a.aux_in) w = w && a32(a.aux_in) && a.ld_aux % 16 == 0;
+  p.vec32_ok = w ? 1 : 0;
   return p;
 }
 
@@ -629,18 +680,28 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   const long long batch = (long long)(a.batch_inner < 1 ? 1 : a.batch_inner) *
                           (a.batch_outer < 1 ? 1 : a.batch_outer);
   const long long tm = (a.M + BM - 1) / BM;
-  const long long t256 = tm * ((a.N + 255) / 256) * batch;
-  const long long t128 = tm * ((a.N + 127) / 128) * batch;
   const int sms = num_sms();
-  auto eff = [&](long long tiles) {
-    long long waves = (tiles + sms - 1) / sms;
-    return (double)tiles / (double)(waves * sms);
-  };
-  // Wider tiles reuse each A tile twice as much; take them unless the narrower tile
-  // wins clearly on wave quantisation.
-  const bool use256 = a.N > 128 && eff(t256) + 0.10 >= eff(t128);
-  if (use256) return launch_tc<256>(a, stream);
-  return launch_tc<128>(a, stream);
+  // Candidate tile widths; score = wave-quantisation efficiency x a mild preference for wide
+  // tiles (each A tile is reused across more columns, and fewer epilogues per FLOP).
+  const int widths[4] = {256, 192, 128, 64};
+  const double pref[4] = {1.00, 0.97, 0.92, 0.80};
+  int best = 128;
+  double best_score = -1.0;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = widths[i];
+    if (bn > 64 && a.N <= bn / 2) continue;
+    const long long tiles = tm * ((a.N + bn - 1) / bn) * batch;
+    const long long waves = (tiles + sms - 1) / sms;
+    const double useful = (double)a.N / (double)(((a.N + bn - 1) / bn) * bn);
+    const double score = (double)tiles / (double)(waves * sms) * useful * pref[i];
+    if (score > best_score) { best_score = score; best = bn; }
+  }
+  switch (best) {
+    case 256: return launch_tc<256>(a, stream);
+    case 192: return launch_tc<192>(a, stream);
+    case 64: return launch_tc<64>(a, stream);
+    default: return launch_tc<128>(a, stream);
+  }
 }
 
 int gemm_last_device_error() {

@@ -235,16 +235,27 @@ ln_param_partials_generic(const T* __restrict__ x, const T* __restrict__ dy,
   scratch[(int64_t)blockIdx.y * 2 * cols + cols + c] = b;
 }
 
+// 32 columns x 8 partial-lanes per block; lanes are folded in a fixed order (reproducible).
 template <typename TG>
-__global__ void ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
-                                TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate) {
-  const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (c >= 2 * cols) return;
+__global__ void __launch_bounds__(256)
+ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
+                TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int64_t c = blockIdx.x * 32ll + cx;
   float t = 0.0f;
-  for (int p = 0; p < nparts; ++p) t += scratch[(int64_t)p * 2 * cols + c];
-  TG* dst = c < cols ? dgamma + c : dbeta + (c - cols);
-  if (accumulate) t += VecIO<TG>::ld(dst);
-  VecIO<TG>::st(dst, t);
+  if (c < 2 * cols)
+    for (int p = py; p < nparts; p += 8) t += scratch[(int64_t)p * 2 * cols + c];
+  sh[py][cx] = t;
+  __syncthreads();
+  if (py == 0 && c < 2 * cols) {
+    float r = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r += sh[i][cx];
+    TG* dst = c < cols ? dgamma + c : dbeta + (c - cols);
+    if (accumulate) r += VecIO<TG>::ld(dst);
+    VecIO<TG>::st(dst, r);
+  }
 }
 
 int bwd_blocks(int64_t rows) {
@@ -396,7 +407,7 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
   if (e != cudaSuccess) return e;
   if (dgamma && dbeta) {
     LT_DISPATCH_DTYPE(grad_dtype, TG, {
-      ln_param_reduce<TG><<<(unsigned)((2 * cols + 255) / 256), 256, 0, s>>>(
+      ln_param_reduce<TG><<<(unsigned)((2 * cols + 31) / 32), 256, 0, s>>>(
           scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
       LT_COUNT_LAUNCH();
     })

@@ -72,10 +72,13 @@ class Linear(Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, input: Tensor, residual: Optional[Tensor] = None,
-                act: Optional[str] = None) -> Tensor:
+                act: Optional[str] = None, sole_consumer: bool = False) -> Tensor:
+        """`sole_consumer=True` promises that nothing else reads `input`; if `input` came out
+        of a Linear with a fused activation, the activation's derivative is then applied in
+        the epilogue of this layer's input-gradient GEMM instead of a separate pass."""
         x = input._t
         if x.is_cuda and (x.dtype == torch.bfloat16 or self.weight._compute is not None):
-            return self._forward_tc(input, residual, act)
+            return self._forward_tc(input, residual, act, sole_consumer)
         out = autograd.matmul(input, self.weight)
         if self.use_bias:
             mm = out
@@ -96,7 +99,7 @@ class Linear(Module):
             out = autograd.add(out, residual)
         return out
 
-    def _forward_tc(self, input, residual, act):
+    def _forward_tc(self, input, residual, act, sole_consumer=False):
         x = input._t
         if x.dtype != torch.bfloat16:
             x = B.cast(x, torch.bfloat16)
@@ -115,6 +118,10 @@ class Linear(Module):
         B.gemm(x, w, bias=b, act=_ACT[act], aux_out=pre, out=y, n_valid=N,
                residual=None if residual is None else residual._t)
         out = Tensor(_data=y)
+        if pre is not None:
+            out._act_ctx = [act, pre, False]
+        fuse_dact = (sole_consumer and input._act_ctx is not None and storage is None
+                     and input._act_ctx[1].is_contiguous())
         weight, bias_p = (storage if storage is not None else self.weight), self.bias
         view_param = self.weight if storage is not None else None
 
@@ -122,12 +129,18 @@ class Linear(Module):
             gt = g._t if g._t.dtype == torch.bfloat16 else g._t.to(torch.bfloat16)
             if residual is not None and residual.requires_grad:
                 autograd.acc_grad(residual, gt)
-            if act is not None:
+            if act is not None and not out._act_ctx[2]:
                 gt = B.ext().unary_backward(B._UN[act], pre, gt)
             if gt.stride(-1) != 1:
                 gt = gt.contiguous()
             if input.requires_grad:
-                autograd.acc_grad(input, B.gemm(gt, w, b_t=True, k_valid=N))
+                if fuse_dact and input.grad is None:
+                    in_act, in_pre, _ = input._act_ctx
+                    autograd.acc_grad(input, B.gemm(gt, w, b_t=True, k_valid=N,
+                                                    act=_DACT[in_act], aux_in=in_pre))
+                    input._act_ctx[2] = True     # derivative already applied
+                else:
+                    autograd.acc_grad(input, B.gemm(gt, w, b_t=True, k_valid=N))
             if weight.requires_grad:
                 if view_param is not None and view_param.grad is None:
                     weight.grad = None

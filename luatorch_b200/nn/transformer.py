@@ -57,9 +57,9 @@ class TransformerBlock(Module):
         normed = self.ln2(x)
         h = self.ffn1(normed, act="gelu")
         if fuse2:
-            x = self.ffn2(h, residual=x)
+            x = self.ffn2(h, residual=x, sole_consumer=True)
         else:
-            x = autograd.add(x, self.drop2(self.ffn2(h)))
+            x = autograd.add(x, self.drop2(self.ffn2(h, sole_consumer=True)))
         return x
 
     def children(self):
