@@ -11,7 +11,7 @@
 // and read with acquire.sys loads.  `epoch` increases by one per collective on every rank.
 // Every wait is bounded; on expiry the kernel records
 // {code, rank, epoch, phase, peer, seen} in `status` (8 ints) and returns without touching
-// data it could not prove complete.  No TMA, no cluster multicast: plain vector ld/st.
+// data it could not prove complete.  Data moves with plain vector ld/st only.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

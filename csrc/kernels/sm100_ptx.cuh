@@ -74,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // ----------------------------------------------------------------------------
-// TMA (tiled bulk tensor loads, no cluster multicast anywhere)
+// TMA: tiled bulk tensor loads, each CTA fetches its own tiles
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
