@@ -31,7 +31,11 @@ constexpr int BM = 128;
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
-constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quadrant, each half the columns
+#ifndef LT_EPI_WARPS
+#define LT_EPI_WARPS 8
+#endif
+constexpr int EPI_WARPS = LT_EPI_WARPS;     // EPI_WARPS/4 warps per TMEM lane quadrant share the columns
+constexpr int EPI_SPLIT = EPI_WARPS / 4;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
@@ -337,8 +341,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // -------------------------------- epilogue --------------------------------
     const int quad = warp_idx & 3;  // TMEM lane quadrant this warp may read
-    const int half = (warp_idx - 2) >> 2;         // which half of the tile's columns
-    constexpr int HALF_COLS = BN / 2;
+    const int half = (warp_idx - 2) >> 2;         // which slice of the tile's columns
+    constexpr int HALF_COLS = BN / EPI_SPLIT;
+#ifndef LT_EPI_CW
+#define LT_EPI_CW 64
+#endif
+    constexpr int EPI_CW = (HALF_COLS % LT_EPI_CW == 0) ? LT_EPI_CW : 32;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -360,13 +368,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const size_t esz = p.c_fp32 ? 4 : 2;
       char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      // TMEM is read in batches of EPI_CW columns: all loads of a batch are issued before the
+      // single wait, so their latencies overlap instead of adding up.
 #pragma unroll 1
-      for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
-        const int col0 = n0 + c0;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
+      for (int cb = half * HALF_COLS; cb < (half + 1) * HALF_COLS; cb += EPI_CW) {
+        if (n0 + cb >= p.N) break;  // uniform across the warp
+        uint32_t rr[EPI_CW];
+#ifndef LT_GEMM_DBG_NO_EPI
+#pragma unroll
+        for (int s = 0; s < EPI_CW / 32; ++s)
+          tmem_ld_32x32(t_row + cb + 32 * s, *reinterpret_cast<uint32_t(*)[32]>(&rr[32 * s]));
         tmem_ld_wait();
+#endif
+#pragma unroll
+        for (int s = 0; s < EPI_CW / 32; ++s) {
+        const int c0 = cb + 32 * s;
+        const int col0 = n0 + c0;
+        if (col0 >= p.N) break;
+        const uint32_t* r = &rr[32 * s];
+#ifdef LT_GEMM_DBG_NO_EPI
+        continue;
+#endif
+#ifdef LT_GEMM_DBG_NO_STORE
+        if (r[0] != 0x7fc12345u) continue;
+#endif
         if (!row_ok) continue;
         if (p.vec_ok && col0 + 32 <= p.N) {
           float v[32];
@@ -446,10 +471,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             store_bf16x32(cp, v, p.vec32_ok);
           }
         } else {
+          // fully unrolled so the accumulator registers are only ever indexed statically
+          // (a dynamic index would force the whole batch into local memory)
+#pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = col0 + i;
             if (col < p.N) epilogue_store_scalar(p, c_base, row, col, __uint_as_float(r[i]));
           }
+        }
         }
       }
       tc_fence_before_sync();

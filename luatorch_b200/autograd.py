@@ -38,7 +38,18 @@ _pending_uses = {}   # id(leaf tensor) -> [tensor, outstanding uses]
 
 
 def zero_graph() -> None:
+    """Drop the tape.  Nodes and their closures reference each other through the tensors
+    they produced (tensor._node -> node.grad_fn -> tensor); the links are cut here so the
+    activations are released by reference counting at once instead of waiting for the cycle
+    collector (which otherwise lets device memory pile up across steps)."""
     global graph
+    for node in graph:
+        t = node.tensor
+        if t is not None and t._node is node:
+            t._node = None
+        node.grad_fn = None
+        node.parents = ()
+        node.tensor = None
     graph = []
     _pending_uses.clear()
 
@@ -133,6 +144,9 @@ def backward(loss: Tensor, grad: Optional[Tensor] = None) -> None:
                 node.tensor.grad = None
             if _pending_uses:
                 _leaf_done(node)
+            # the closure holds the activations saved for this node: release them now
+            node.grad_fn = None
+            node.parents = ()
 
 
 def zero_grad(tensors: Sequence[Tensor]) -> None:
