@@ -22,7 +22,13 @@ namespace lt {
 using namespace ptx;
 
 extern std::atomic<uint64_t> g_attn_launches;
-extern __device__ int g_attn_error;
+// Status word of the backward kernels (device symbols are per translation unit).
+static __device__ int g_attn_error = 0;
+int attention_bwd_device_error() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int));
+  return v;
+}
 
 namespace attn_detail {
 bool make_qkv_map(CUtensorMap* map, const void* base, int D, int S, int H, int B, int64_t ss,
@@ -33,7 +39,8 @@ namespace {
 
 constexpr int BT = 128;                  // tile edge (queries and keys)
 constexpr int CHUNK_BYTES = 128 * 128;   // 128 rows x 64 bf16
-constexpr int NUM_THREADS = 192;
+constexpr int COMPUTE_WARPS = 8;          // two per TMEM lane quadrant: each takes half of the key columns
+constexpr int NUM_THREADS = 64 + 32 * COMPUTE_WARPS;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -82,47 +89,74 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 
 // Rebuild P and dS for one query row from the S / dP accumulators in TMEM and store them
 // (bf16) into the swizzled [query row][key] shared-memory tiles.
+template <bool WRITE_P, bool MASKED>
+__device__ __forceinline__ void rebuild_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32],
+                                              int valid, float lse_l2, float delta, float c,
+                                              float scale, uint8_t* p_dst, uint8_t* ds_dst,
+                                              int c32, int row) {
+  uint32_t pp[16], dd[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float p0 = ex2(fmaf(__uint_as_float(s[i]), c, -lse_l2));
+    float p1 = ex2(fmaf(__uint_as_float(s[i + 1]), c, -lse_l2));
+    if (MASKED) {
+      p0 = (i < valid) ? p0 : 0.0f;
+      p1 = (i + 1 < valid) ? p1 : 0.0f;
+    }
+    const float d0 = p0 * (__uint_as_float(dp[i]) - delta) * scale;
+    const float d1 = p1 * (__uint_as_float(dp[i + 1]) - delta) * scale;
+    __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+    pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
+    dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int chunk16 = (((c32 & 1) * 4 + t) ^ (row & 7)) * 16;
+    if (WRITE_P)
+      *reinterpret_cast<uint4*>(p_dst + chunk16) =
+          make_uint4(pp[4 * t], pp[4 * t + 1], pp[4 * t + 2], pp[4 * t + 3]);
+    *reinterpret_cast<uint4*>(ds_dst + chunk16) =
+        make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
+  }
+}
+
+// This warp's half (`col_half`) of one query row: two 32-column chunks of S and dP.  No
+// reduction across columns is needed in backward, so the halves are independent.  The second
+// chunk's TMEM reads are in flight while the first is processed.
 template <bool WRITE_P>
 __device__ __forceinline__ void rebuild_row(uint32_t tmem_s, uint32_t tmem_dp, uint32_t lane_base,
-                                            int row, int valid, float lse_l2, float delta,
-                                            float c, float scale, uint8_t* p_tile,
-                                            uint8_t* ds_tile) {
-  const int row_off = (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll 1
-  for (int c32 = 0; c32 < 4; ++c32) {
-    uint32_t s[32], dp[32];
-    tmem_ld_32x32(tmem_s + lane_base + c32 * 32, s);
-    tmem_ld_32x32(tmem_dp + lane_base + c32 * 32, dp);
+                                            int row, int valid, bool masked, float lse_l2,
+                                            float delta, float c, float scale, uint8_t* p_tile,
+                                            uint8_t* ds_tile, int col_half) {
+  const int row_off = (row >> 3) * 1024 + (row & 7) * 128 + col_half * CHUNK_BYTES;
+  const int col0 = col_half * 64;
+  uint32_t s0[32], d0[32], s1[32], d1[32];
+  tmem_ld_32x32(tmem_s + lane_base + col0, s0);
+  tmem_ld_32x32(tmem_dp + lane_base + col0, d0);
+  tmem_ld_wait();
+  tmem_ld_32x32(tmem_s + lane_base + col0 + 32, s1);
+  tmem_ld_32x32(tmem_dp + lane_base + col0 + 32, d1);
+  if (masked) {
+    rebuild_chunk<WRITE_P, true>(s0, d0, valid - col0, lse_l2, delta, c, scale, p_tile + row_off,
+                                 ds_tile + row_off, 0, row);
     tmem_ld_wait();
-    uint32_t pp[16], dd[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float p0 = (c32 * 32 + i < valid) ? ex2(__uint_as_float(s[i]) * c - lse_l2) : 0.0f;
-      float p1 = (c32 * 32 + i + 1 < valid) ? ex2(__uint_as_float(s[i + 1]) * c - lse_l2) : 0.0f;
-      float d0 = p0 * (__uint_as_float(dp[i]) - delta) * scale;
-      float d1 = p1 * (__uint_as_float(dp[i + 1]) - delta) * scale;
-      __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
-      pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
-      dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
-    }
-    const int chunk_off = (c32 >> 1) * CHUNK_BYTES + row_off;
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int chunk16 = (((c32 & 1) * 4 + t) ^ (row & 7)) * 16;
-      if (WRITE_P)
-        *reinterpret_cast<uint4*>(p_tile + chunk_off + chunk16) =
-            make_uint4(pp[4 * t], pp[4 * t + 1], pp[4 * t + 2], pp[4 * t + 3]);
-      *reinterpret_cast<uint4*>(ds_tile + chunk_off + chunk16) =
-          make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
-    }
+    rebuild_chunk<WRITE_P, true>(s1, d1, valid - col0 - 32, lse_l2, delta, c, scale,
+                                 p_tile + row_off, ds_tile + row_off, 1, row);
+  } else {
+    rebuild_chunk<WRITE_P, false>(s0, d0, 32, lse_l2, delta, c, scale, p_tile + row_off,
+                                  ds_tile + row_off, 0, row);
+    tmem_ld_wait();
+    rebuild_chunk<WRITE_P, false>(s1, d1, 32, lse_l2, delta, c, scale, p_tile + row_off,
+                                  ds_tile + row_off, 1, row);
   }
 }
 
 // Store one accumulator row (D fp32 columns in TMEM) as bf16.
 template <int D>
-__device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst) {
-#pragma unroll
-  for (int c32 = 0; c32 < D / 32; ++c32) {
+__device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst, int first) {
+  // the two warps that share a lane quadrant take alternate 32-column chunks
+#pragma unroll 1
+  for (int c32 = first; c32 < D / 32; c32 += 2) {
     uint32_t r[32];
     tmem_ld_32x32(taddr + c32 * 32, r);
     tmem_ld_wait();
@@ -197,8 +231,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(smem_u32(&str_empty[i]), 1);
     }
     mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_empty), 128);
-    mbar_init(smem_u32(pds_full), 128);
+    mbar_init(smem_u32(s_empty), 32 * COMPUTE_WARPS);
+    mbar_init(smem_u32(pds_full), 32 * COMPUTE_WARPS);
     mbar_init(smem_u32(pds_empty), 1);
     mbar_init(smem_u32(acc_full), 1);
     fence_mbar_init();
@@ -350,6 +384,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   } else {
     const int quad = warp_idx & 3;
+    const int col_half = (warp_idx - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
     bool ok = true;
@@ -359,6 +394,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int qi = q_tile * BT + row, k0 = k_tile * BT;
       int valid = 0;
       float lse_l2 = 0.0f, delta = 0.0f;
+      // uniform per tile: does any element of this (query tile, key tile) pair need masking?
+      const bool tile_masked = (p.causal && k0 + BT - 1 > q_tile * BT) || (k0 + BT > p.S) ||
+                               (q_tile * BT + BT > p.S);
       if (qi < p.S) {
         int lim = p.S - k0;
         if (p.causal) { int cl = qi - k0 + 1; lim = cl < lim ? cl : lim; }
@@ -373,8 +411,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         break;
       }
       tc_fence_after_sync();
-      rebuild_row<DKDV>(tmem_s, tmem_dp, lane_base, row, valid, lse_l2, delta, p.scale_log2,
-                        p.scale, smem + L::OFF_P, smem + L::OFF_DS);
+      rebuild_row<DKDV>(tmem_s, tmem_dp, lane_base, row, valid, tile_masked, lse_l2, delta,
+                        p.scale_log2, p.scale, smem + L::OFF_P, smem + L::OFF_DS, col_half);
       tc_fence_before_sync();
       mbar_arrive(smem_u32(s_empty));
       fence_proxy_async();
@@ -388,17 +426,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       __nv_bfloat16* d0 = in_range ? p.out0 + (long long)b * p.o0_sb + (long long)gi * p.o0_ss +
                                          (long long)h * p.o0_sh
                                    : nullptr;
-      store_acc_row<D>(tmem_acc0 + lane_base, d0);
+      store_acc_row<D>(tmem_acc0 + lane_base, d0, col_half);
       if (DKDV) {
         __nv_bfloat16* d1 = in_range ? p.out1 + (long long)b * p.o1_sb + (long long)gi * p.o1_ss +
                                            (long long)h * p.o1_sh
                                      : nullptr;
-        store_acc_row<D>(tmem_acc1 + lane_base, d1);
+        store_acc_row<D>(tmem_acc1 + lane_base, d1, col_half);
       }
     } else if (ok && n_it == 0) {
       // a key tile no query attends to (cannot happen for causal self-attention): zero output
       const int gi = own * BT + row;
-      if (gi < p.S) {
+      if (gi < p.S && col_half == 0) {
         __nv_bfloat16* d0 = p.out0 + (long long)b * p.o0_sb + (long long)gi * p.o0_ss +
                             (long long)h * p.o0_sh;
         for (int i = 0; i < D; ++i) d0[i] = __float2bfloat16(0.0f);

@@ -22,10 +22,11 @@ using namespace ptx;
 std::atomic<uint64_t> g_attn_launches{0};
 __device__ int g_attn_error = 0;
 
+int attention_bwd_device_error();  // attention_bwd.cu
 int attention_last_device_error() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int));
-  return v;
+  return v != 0 ? v : attention_bwd_device_error();
 }
 uint64_t attention_launch_count() { return g_attn_launches.load(); }
 
@@ -76,6 +77,61 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+
+// Row maximum over one 32-column chunk; `valid` = number of leading columns of this chunk
+// that are inside the causal / sequence bounds (only consulted when `masked`).
+__device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], float mx, bool masked,
+                                           int valid) {
+  if (!masked) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2)
+      mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+  }
+  return mx;
+}
+
+// p = 2^(s*c - mc) for one chunk, written as bf16 into the swizzled operand-A tile; returns
+// the chunk's row sum.
+__device__ __forceinline__ float chunk_exp_store(const uint32_t (&r)[32], float c, float mc,
+                                                 bool masked, int valid, uint8_t* p_row, int c32,
+                                                 int row) {
+  uint32_t packed[16];
+  float sum0 = 0.0f, sum1 = 0.0f;
+  if (!masked) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const float p0 = ex2(fmaf(__uint_as_float(r[i]), c, -mc));
+      const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, -mc));
+      sum0 += p0;
+      sum1 += p1;
+      __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+      packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const float p0 = (i < valid) ? ex2(fmaf(__uint_as_float(r[i]), c, -mc)) : 0.0f;
+      const float p1 = (i + 1 < valid) ? ex2(fmaf(__uint_as_float(r[i + 1]), c, -mc)) : 0.0f;
+      sum0 += p0;
+      sum1 += p1;
+      __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+      packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
+    }
+  }
+  uint8_t* dst = p_row + (c32 >> 1) * CHUNK_BYTES;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int chunk16 = ((c32 & 1) * 4 + t) ^ (row & 7);
+    *reinterpret_cast<uint4*>(dst + chunk16 * 16) =
+        make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+  }
+  return sum0 + sum1;
 }
 
 struct FwdParams {
@@ -290,19 +346,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (p.causal) { int cl = qi - k0 + 1; lim = cl < lim ? cl : lim; }
         valid = lim < 0 ? 0 : (lim > BN ? BN : lim);
       }
-      // pass 1: row maximum
+      // pass 1: row maximum.  TMEM reads are double buffered: the next 32-column chunk is in
+      // flight while the current one is reduced.
       float mx = m;
-#pragma unroll 1
-      for (int c32 = 0; c32 < 4; ++c32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_base + st * BN + c32 * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sv = __uint_as_float(r[i]);
-          if (c32 * 32 + i < valid) mx = fmaxf(mx, sv);
-        }
-      }
+      uint32_t ra[32], rb[32];
+      const uint32_t s_addr = tmem_s + lane_base + st * BN;
+      tmem_ld_32x32(s_addr, ra);
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr + 32, rb);
+      mx = chunk_max(ra, mx, need_mask, valid);
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr + 64, ra);
+      mx = chunk_max(rb, mx, need_mask, valid - 32);
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr + 96, rb);
+      mx = chunk_max(ra, mx, need_mask, valid - 64);
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr, ra);            // first chunk of pass 2, lands during the O fold
+      mx = chunk_max(rb, mx, need_mask, valid - 96);
       const float m_new = mx;
       const float alpha = (m == -INFINITY) ? 0.0f : ex2((m - m_new) * c);
       // fold in the previous tile's P V product, then rescale to the new maximum
@@ -329,28 +390,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // pass 2: exponentials -> P (bf16, swizzled operand-A layout) + row sum
       const float mc = (m_new == -INFINITY) ? 0.0f : m_new * c;
       float rsum = 0.0f;
-#pragma unroll 1
-      for (int c32 = 0; c32 < 4; ++c32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_base + st * BN + c32 * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = (c32 * 32 + i < valid) ? ex2(__uint_as_float(r[i]) * c - mc) : 0.0f;
-          float p1 = (c32 * 32 + i + 1 < valid) ? ex2(__uint_as_float(r[i + 1]) * c - mc) : 0.0f;
-          rsum += p0 + p1;
-          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
-        }
-        uint8_t* dst = p_row + (c32 >> 1) * CHUNK_BYTES;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int chunk16 = ((c32 & 1) * 4 + t) ^ (row & 7);
-          *reinterpret_cast<uint4*>(dst + chunk16 * 16) =
-              make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
-        }
-      }
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr + 32, rb);
+      rsum += chunk_exp_store(ra, c, mc, need_mask, valid, p_row, 0, row);
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr + 64, ra);
+      rsum += chunk_exp_store(rb, c, mc, need_mask, valid - 32, p_row, 1, row);
+      tmem_ld_wait();
+      tmem_ld_32x32(s_addr + 96, rb);
+      rsum += chunk_exp_store(ra, c, mc, need_mask, valid - 64, p_row, 2, row);
+      tmem_ld_wait();
+      rsum += chunk_exp_store(rb, c, mc, need_mask, valid - 96, p_row, 3, row);
       l += rsum;
       m = m_new;
       tc_fence_before_sync();
