@@ -23,7 +23,7 @@ namespace {
 std::atomic<uint64_t> g_comm_launches{0};
 
 constexpr int THREADS = 512;
-constexpr int DEFAULT_BLOCKS = 64;
+constexpr int DEFAULT_BLOCKS = 296;   // two CTAs per SM on a 148-SM part
 constexpr int MAX_WORLD = 16;
 constexpr int SLOT_START = 0;
 constexpr int SLOT_DONE = 16;
@@ -42,8 +42,7 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
+               : "l"(p));
   return v;
 }
 __device__ __forceinline__ void st_peer16(void* p, uint4 v) {
@@ -155,15 +154,22 @@ __device__ __forceinline__ int find_segment(const int64_t* seg_end, int nseg, in
   return lo;
 }
 
-__device__ __forceinline__ void adam8(float* master, float* m, float* v, int64_t e,
+// State of 8 consecutive parameters, loaded early so the HBM reads overlap the NVLink reads.
+struct Adam8State { float4 p0, p1, m0, m1, v0, v1; };
+__device__ __forceinline__ Adam8State adam8_load(const float* master, const float* m, const float* v,
+                                                 long long e) {
+  Adam8State s;
+  s.p0 = *reinterpret_cast<const float4*>(master + e); s.p1 = *reinterpret_cast<const float4*>(master + e + 4);
+  s.m0 = *reinterpret_cast<const float4*>(m + e); s.m1 = *reinterpret_cast<const float4*>(m + e + 4);
+  s.v0 = *reinterpret_cast<const float4*>(v + e); s.v1 = *reinterpret_cast<const float4*>(v + e + 4);
+  return s;
+}
+__device__ __forceinline__ void adam8(float* master, float* m, float* v, long long e, const Adam8State& s,
                                       const float (&g)[8], float wd, const AdamArgs& a,
                                       float (&p_out)[8]) {
-  float4 p0 = *reinterpret_cast<float4*>(master + e), p1 = *reinterpret_cast<float4*>(master + e + 4);
-  float4 m0 = *reinterpret_cast<float4*>(m + e), m1 = *reinterpret_cast<float4*>(m + e + 4);
-  float4 v0 = *reinterpret_cast<float4*>(v + e), v1 = *reinterpret_cast<float4*>(v + e + 4);
-  float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-  float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-  float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  float p[8] = {s.p0.x, s.p0.y, s.p0.z, s.p0.w, s.p1.x, s.p1.y, s.p1.z, s.p1.w};
+  float mm[8] = {s.m0.x, s.m0.y, s.m0.z, s.m0.w, s.m1.x, s.m1.y, s.m1.z, s.m1.w};
+  float vv[8] = {s.v0.x, s.v0.y, s.v0.z, s.v0.w, s.v1.x, s.v1.y, s.v1.z, s.v1.w};
   const float decay = 1.0f - a.lr * wd;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -216,6 +222,7 @@ allreduce_adamw_kernel(const KArgs k) {
   const long long base = k.elem_offset + (sharded ? (long long)k.rank * span : 0);
   for (long long i = tid; i < span / 8; i += nthreads) {
     const long long e = base + i * 8;
+    const Adam8State st = adam8_load(k.master, k.m, k.v, e);   // HBM reads go out first
     uint4 part[WORLD ? WORLD : MAX_WORLD];
 #pragma unroll
     for (int q = 0; q < (WORLD ? WORLD : MAX_WORLD); ++q) {
@@ -235,7 +242,7 @@ allreduce_adamw_kernel(const KArgs k) {
     }
     const float wd = k.nseg > 0 ? k.seg_wd[find_segment(k.seg_end, k.nseg, e)] : 0.0f;
     float p[8];
-    adam8(k.master, k.m, k.v, e, g, wd, k.adam, p);
+    adam8(k.master, k.m, k.v, e, st, g, wd, k.adam, p);
     const uint4 packed = pack_bf16x8(p);
     if (sharded) {
 #pragma unroll

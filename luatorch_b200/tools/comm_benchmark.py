@@ -1,0 +1,102 @@
+"""Roofline of the fused all-reduce + AdamW kernels against the NVLink bound and against NCCL.
+
+    python -m torch.distributed.run --nproc-per-node N -m luatorch_b200.tools.comm_benchmark
+
+For each bucket size it times (CUDA events, max over ranks, after warm-up)
+  fused-sharded     one launch: reduce-scatter over peer memory + shard AdamW + bf16 parameter
+                    all-gather by peer stores
+  fused-replicated  one launch: every rank reduces the whole bucket and updates its replica
+  nccl + adamw      ncclAllReduce on the bf16 gradients, then the flat AdamW launch
+and reports the achieved fraction of the roofline: the slower of (bytes that must cross
+NVLink per GPU / 770 GB/s per direction, the measured peer-copy rate of this machine class) and
+(local HBM traffic of the AdamW update / measured copy bandwidth).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+NVLINK_BPS = 770e9
+
+
+def main():
+    import luatorch_b200 as lf
+    from luatorch_b200 import _backend as B
+    from luatorch_b200.distributed import comm
+    comm.init()
+    rank, world = comm.rank(), comm.world_size()
+    C = B.ext()
+    hbm = 6.65e12
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        hbm = json.load(open(p))["hbm_gbs"] * 1e9
+    sizes_mb = [1, 8, 32, 128, 311]
+    n_max = max(sizes_mb) * 1024 * 1024 // 2
+    grad_buf = comm.SymmetricBuffer(n_max * 2)
+    shadow_buf = comm.SymmetricBuffer(n_max * 2)
+    master = torch.randn(n_max, device="cuda")
+    m = torch.zeros(n_max, device="cuda")
+    v = torch.zeros(n_max, device="cuda")
+    grad = grad_buf.typed(torch.bfloat16)[:n_max]
+    shadow = shadow_buf.typed(torch.bfloat16)[:n_max]
+    grad.copy_(torch.randn(n_max, device="cuda") * 0.01)
+    seg_end = torch.tensor([n_max], device="cuda", dtype=torch.int64)
+    seg_wd = torch.tensor([0.1], device="cuda")
+    status = comm.status_buffer()
+    blocks = int(os.environ.get("LT_COMM_BLOCKS", "0"))   # 0 = the kernel's default
+
+    def timed(fn, iters=10, warmup=3):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if rank == 0:
+        print("world %d; NVLink bound %.0f GB/s per direction per GPU; HBM %.0f GB/s" % (world, NVLINK_BPS / 1e9, hbm / 1e9))
+    for mb in sizes_mb:
+        n = mb * 1024 * 1024 // 2 // (8 * world) * (8 * world)
+        nbytes = n * 2
+
+        def fused(mode):
+            C.allreduce_adamw(grad_buf.ptrs, grad_buf.signal_ptrs, rank, world, 0, n, master, shadow_buf.ptrs, m, v,
+                              seg_end, seg_wd, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.05, 1.0 / world, comm.next_epoch(), mode,
+                              blocks, status)
+
+        def nccl_path():
+            g = grad[:n]
+            dist.all_reduce(g)
+            C.adamw_flat(master[:n], shadow[:n], g, m[:n], v[:n], seg_end, seg_wd, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.05,
+                         1.0 / world, None)
+
+        rows = []
+        for name, fn, link_bytes, hbm_bytes in [
+            ("fused-sharded", lambda: fused(1), nbytes * (world - 1) / world, n / world * 26.0 + nbytes / world * 2),
+            ("fused-replicated", lambda: fused(0), nbytes * (world - 1), n * 26.0 + nbytes),
+            ("nccl + adamw", nccl_path, nbytes * (world - 1) / world, n * 28.0),
+        ]:
+            ms = timed(fn)
+            bound_s = max(link_bytes / NVLINK_BPS, hbm_bytes / hbm)
+            rows.append((name, ms, bound_s * 1e3 / ms if ms > 0 else 0.0))
+        comm.check_status()
+        if rank == 0:
+            print("bucket %4d MB (bf16 grads): " % mb + "  ".join("%s %.3f ms (%.0f%% of roofline)" % (a, b, 100 * c) for a, b, c in rows), flush=True)
+    dist.barrier()
+    comm.destroy()
+
+
+if __name__ == "__main__":
+    main()
