@@ -20,6 +20,7 @@
 #include <atomic>
 #include <mutex>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace lt {
 
@@ -183,6 +184,135 @@ __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float* v,
   }
 }
 
+// Epilogue of one 128 x BN accumulator tile: this warp's 32 rows (TMEM lane quadrant `quad`)
+// and column slice `half` of EPI_SPLIT, read from TMEM address `t_row`, written to C.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_row, int m0, int n0,
+                                              int bi, int bo, int quad, int half, int lane) {
+  constexpr int HALF_COLS = BN / EPI_SPLIT;
+#ifndef LT_EPI_CW
+#define LT_EPI_CW 64
+#endif
+  constexpr int EPI_CW = (HALF_COLS % LT_EPI_CW == 0) ? LT_EPI_CW : 32;
+  const long long row = m0 + quad * 32 + lane;
+  const bool row_ok = row < p.M;
+  const size_t esz = p.c_fp32 ? 4 : 2;
+  char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
+  // TMEM is read in batches of EPI_CW columns: all loads of a batch are issued before the
+  // single wait, so their latencies overlap instead of adding up.
+#pragma unroll 1
+  for (int cb = half * HALF_COLS; cb < (half + 1) * HALF_COLS; cb += EPI_CW) {
+    if (n0 + cb >= p.N) break;  // uniform across the warp
+    uint32_t rr[EPI_CW];
+#ifndef LT_GEMM_DBG_NO_EPI
+#pragma unroll
+    for (int s = 0; s < EPI_CW / 32; ++s)
+      tmem_ld_32x32(t_row + cb + 32 * s, *reinterpret_cast<uint32_t(*)[32]>(&rr[32 * s]));
+    tmem_ld_wait();
+#endif
+#pragma unroll
+    for (int s = 0; s < EPI_CW / 32; ++s) {
+    const int c0 = cb + 32 * s;
+    const int col0 = n0 + c0;
+    if (col0 >= p.N) break;
+    const uint32_t* r = &rr[32 * s];
+#ifdef LT_GEMM_DBG_NO_EPI
+    continue;
+#endif
+#ifdef LT_GEMM_DBG_NO_STORE
+    if (r[0] != 0x7fc12345u) continue;
+#endif
+    if (!row_ok) continue;
+    if (p.vec_ok && col0 + 32 <= p.N) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      if (p.alpha != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+      }
+      if (p.bias) {
+        if (p.bias_fp32) {
+          const float4* bp = reinterpret_cast<const float4*>((const float*)p.bias + col0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 bv = __ldg(bp + i);
+            v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
+          }
+        } else {
+          const uint4* bp =
+              reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.bias + col0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float f[8];
+            unpack8(__ldg(bp + i), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
+          }
+        }
+      }
+      if (p.act == GEMM_ACT_GELU || p.act == GEMM_ACT_RELU) {
+        if (p.aux_out) {
+          store_bf16x32(p.aux_out + row * p.ldc + col0, v, p.vec32_ok);
+        }
+        if (p.act == GEMM_ACT_GELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+        }
+      } else if (p.act == GEMM_ACT_DGELU || p.act == GEMM_ACT_DRELU) {
+        float x[32];
+        load_bf16x32(p.aux_in + row * p.ld_aux + col0, x, p.vec32_ok);
+        if (p.act == GEMM_ACT_DGELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= dgelu_f(x[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = x[i] > 0.0f ? v[i] : 0.0f;
+        }
+      }
+      if (p.residual) {
+        float x[32];
+        load_bf16x32(p.residual + row * p.ldr + col0, x, p.vec32_ok);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += x[i];
+      }
+      if (p.c_fp32) {
+        float4* cp = reinterpret_cast<float4*>((float*)c_base + row * p.ldc + col0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          if (p.accumulate) {
+            float4 old = cp[i];
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          cp[i] = o;
+        }
+      } else {
+        __nv_bfloat16* cp = (__nv_bfloat16*)c_base + row * p.ldc + col0;
+        if (p.accumulate) {
+          float x[32];
+          load_bf16x32(cp, x, p.vec32_ok);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += x[i];
+        }
+        store_bf16x32(cp, v, p.vec32_ok);
+      }
+    } else {
+      // fully unrolled so the accumulator registers are only ever indexed statically
+      // (a dynamic index would force the whole batch into local memory)
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int col = col0 + i;
+        if (col < p.N) epilogue_store_scalar(p, c_base, row, col, __uint_as_float(r[i]));
+      }
+    }
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -342,11 +472,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // -------------------------------- epilogue --------------------------------
     const int quad = warp_idx & 3;  // TMEM lane quadrant this warp may read
     const int half = (warp_idx - 2) >> 2;         // which slice of the tile's columns
-    constexpr int HALF_COLS = BN / EPI_SPLIT;
-#ifndef LT_EPI_CW
-#define LT_EPI_CW 64
-#endif
-    constexpr int EPI_CW = (HALF_COLS % LT_EPI_CW == 0) ? LT_EPI_CW : 32;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -363,124 +488,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         break;
       }
       tc_fence_after_sync();
-      const long long row = m0 + quad * 32 + lane;
-      const bool row_ok = row < p.M;
-      const size_t esz = p.c_fp32 ? 4 : 2;
-      char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-      // TMEM is read in batches of EPI_CW columns: all loads of a batch are issued before the
-      // single wait, so their latencies overlap instead of adding up.
-#pragma unroll 1
-      for (int cb = half * HALF_COLS; cb < (half + 1) * HALF_COLS; cb += EPI_CW) {
-        if (n0 + cb >= p.N) break;  // uniform across the warp
-        uint32_t rr[EPI_CW];
-#ifndef LT_GEMM_DBG_NO_EPI
-#pragma unroll
-        for (int s = 0; s < EPI_CW / 32; ++s)
-          tmem_ld_32x32(t_row + cb + 32 * s, *reinterpret_cast<uint32_t(*)[32]>(&rr[32 * s]));
-        tmem_ld_wait();
-#endif
-#pragma unroll
-        for (int s = 0; s < EPI_CW / 32; ++s) {
-        const int c0 = cb + 32 * s;
-        const int col0 = n0 + c0;
-        if (col0 >= p.N) break;
-        const uint32_t* r = &rr[32 * s];
-#ifdef LT_GEMM_DBG_NO_EPI
-        continue;
-#endif
-#ifdef LT_GEMM_DBG_NO_STORE
-        if (r[0] != 0x7fc12345u) continue;
-#endif
-        if (!row_ok) continue;
-        if (p.vec_ok && col0 + 32 <= p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.alpha != 1.0f) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
-          }
-          if (p.bias) {
-            if (p.bias_fp32) {
-              const float4* bp = reinterpret_cast<const float4*>((const float*)p.bias + col0);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 bv = __ldg(bp + i);
-                v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
-              }
-            } else {
-              const uint4* bp =
-                  reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.bias + col0);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float f[8];
-                unpack8(__ldg(bp + i), f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
-              }
-            }
-          }
-          if (p.act == GEMM_ACT_GELU || p.act == GEMM_ACT_RELU) {
-            if (p.aux_out) {
-              store_bf16x32(p.aux_out + row * p.ldc + col0, v, p.vec32_ok);
-            }
-            if (p.act == GEMM_ACT_GELU) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
-            }
-          } else if (p.act == GEMM_ACT_DGELU || p.act == GEMM_ACT_DRELU) {
-            float x[32];
-            load_bf16x32(p.aux_in + row * p.ld_aux + col0, x, p.vec32_ok);
-            if (p.act == GEMM_ACT_DGELU) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= dgelu_f(x[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = x[i] > 0.0f ? v[i] : 0.0f;
-            }
-          }
-          if (p.residual) {
-            float x[32];
-            load_bf16x32(p.residual + row * p.ldr + col0, x, p.vec32_ok);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += x[i];
-          }
-          if (p.c_fp32) {
-            float4* cp = reinterpret_cast<float4*>((float*)c_base + row * p.ldc + col0);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-              if (p.accumulate) {
-                float4 old = cp[i];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              cp[i] = o;
-            }
-          } else {
-            __nv_bfloat16* cp = (__nv_bfloat16*)c_base + row * p.ldc + col0;
-            if (p.accumulate) {
-              float x[32];
-              load_bf16x32(cp, x, p.vec32_ok);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] += x[i];
-            }
-            store_bf16x32(cp, v, p.vec32_ok);
-          }
-        } else {
-          // fully unrolled so the accumulator registers are only ever indexed statically
-          // (a dynamic index would force the whole batch into local memory)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            if (col < p.N) epilogue_store_scalar(p, c_base, row, col, __uint_as_float(r[i]));
-          }
-        }
-        }
-      }
+      epilogue_tile<BN>(p, tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN, m0, n0, bi, bo,
+                        quad, half, lane);
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -492,6 +501,233 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp_idx == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (two SMs) owns one 256 x BN output tile.  CTA r holds
+// rows [128 r, 128 r + 128) of the A tile, columns [r BN/2, (r+1) BN/2) of the B tile and the
+// accumulator rows of its half; the even CTA issues tcgen05.mma.cta_group::2 for both.  Each SM
+// therefore stages and reads only half of B, which halves the shared-memory traffic per FLOP
+// relative to the single-CTA kernel.  Barrier protocol per stage:
+//   full  (even CTA only): its producer arms it with the bytes of BOTH CTAs' loads; the odd
+//          CTA's loads credit their bytes to the same barrier through its cluster address;
+//   empty (both CTAs): the MMA thread commits to the local one and to the peer's, so each
+//          producer refills its own stage when the MMAs that read it have retired;
+//   tmem_full (both CTAs) / tmem_empty (even CTA, one arrive per epilogue warp of both CTAs).
+// ------------------------------------------------------------------------------
+#ifndef LT_PAIR_KSUB
+#define LT_PAIR_KSUB 1
+#endif
+template <int BN>
+struct PairCfg {
+  static constexpr int KSUB = LT_PAIR_KSUB;             // 64-wide k blocks per pipeline stage
+  static constexpr int B_ROWS = BN / 2;                 // B-tile rows (n) held by one CTA
+  static constexpr int B_SUB_BYTES = B_ROWS * BK * 2;
+  static constexpr int A_STAGE = A_STAGE_BYTES * KSUB;
+  static constexpr int B_STAGE_BYTES = B_SUB_BYTES * KSUB;
+  static constexpr int STAGE_BYTES = A_STAGE + B_STAGE_BYTES;
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;  // 6 at BN=256, 8 at BN=128 (KSUB 1)
+  static constexpr int TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
+  using Cfg = PairCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * Cfg::A_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_base_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_holder + 1);
+
+  const int warp_idx = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_cta_rank();   // 0 = even CTA (issues the MMAs), 1 = odd
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EPI_WARPS);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp_idx == 1) {
+    tmem_alloc_pair(smem_u32(tmem_base_holder), Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();          // the peer's barriers exist before anything is sent to them
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_holder;
+
+  const int num_kb = (p.K + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;     // tiles_m counts 256-row pair tiles
+  const int total_tiles = tiles_per_batch * p.batch_total;
+
+  if (warp_idx == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
+        const int b = tile / tiles_per_batch;
+        const int t = tile - b * tiles_per_batch;
+        const int m0 = (t % p.tiles_m) * (2 * BM) + (int)cta_rank * BM;
+        const int n0 = (t / p.tiles_m) * BN + (int)cta_rank * Cfg::B_ROWS;
+        const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag,
+                                 &g_gemm_error, 11)) {
+            ok = false;
+            break;
+          }
+          // bytes of both CTAs land on the even CTA's barrier
+          const uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
+#ifdef LT_GEMM_DBG_NO_TMA
+          if (cta_rank == 0) mbar_arrive(smem_u32(&full_bar[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          continue;
+#endif
+          if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * Cfg::STAGE_BYTES);
+#pragma unroll
+          for (int sub = 0; sub < Cfg::KSUB; ++sub) {
+            const uint32_t sa = smem_u32(smem_a + stage * Cfg::A_STAGE + sub * A_STAGE_BYTES);
+            const uint32_t sb = smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES + sub * Cfg::B_SUB_BYTES);
+            const int k0 = (kb * Cfg::KSUB + sub) * BK;   // past K: the load returns zeros
+            if (!p.a_mn) {
+              tma_load_4d_pair(sa, &tmap_a, fb, k0, m0, bi, bo);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c)
+                tma_load_4d_pair(sa + c * (64 * BK * 2), &tmap_a, fb, m0 + 64 * c, k0, bi, bo);
+            }
+            if (!p.b_mn) {
+              tma_load_4d_pair(sb, &tmap_b, fb, k0, n0, bi, bo);
+            } else {
+#pragma unroll
+              for (int c = 0; c < Cfg::B_ROWS / 64; ++c)
+                tma_load_4d_pair(sb + c * (64 * BK * 2), &tmap_b, fb, n0 + 64 * c, k0, bi, bo);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp_idx == 1) {
+    // ----------------------- MMA issuer (even CTA only) -----------------------
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = make_idesc_bf16(2 * BM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? 64 * BK * 2 : 16, b_lbo = p.b_mn ? 64 * BK * 2 : 16;
+      const uint32_t a_step = p.a_mn ? (2048 >> 4) : (32 >> 4);
+      const uint32_t b_step = p.b_mn ? (2048 >> 4) : (32 >> 4);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
+        if (!mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag,
+                               &g_gemm_error, 12)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag, &g_gemm_error,
+                                 13)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int sub = 0; sub < Cfg::KSUB; ++sub) {
+            const uint64_t a_desc = make_smem_desc_sw128(
+                smem_u32(smem_a + stage * Cfg::A_STAGE + sub * A_STAGE_BYTES), a_lbo, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(
+                smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES + sub * Cfg::B_SUB_BYTES), b_lbo, 1024);
+#pragma unroll
+            for (int j = 0; j < BK / UMMA_K; ++j) {
+#ifdef LT_GEMM_DBG_NO_MMA
+              continue;
+#endif
+              umma_bf16_pair(d_tmem, a_desc + (uint64_t)(j * a_step),
+                             b_desc + (uint64_t)(j * b_step), idesc,
+                             (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
+            }
+          }
+          // the stage is free in both CTAs once these MMAs have retired
+          umma_commit_pair(smem_u32(&empty_bar[stage]));
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(smem_u32(&tmem_full_bar[acc]));
+        umma_commit_pair(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quad = warp_idx & 3;
+    const int half = (warp_idx - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
+      const int b = tile / tiles_per_batch;
+      const int t = tile - b * tiles_per_batch;
+      const int m0 = (t % p.tiles_m) * (2 * BM) + (int)cta_rank * BM;
+      const int n0 = (t / p.tiles_m) * BN;
+      const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+      if (!mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, &g_gemm_error,
+                             14)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      epilogue_tile<BN>(p, tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN, m0, n0, bi, bo,
+                        quad, half, lane);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();          // neither CTA frees TMEM or leaves while the other still works
+  cluster_wait();
+  if (warp_idx == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -673,6 +909,91 @@ cudaError_t launch_tc(const GemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// Number of CTA pairs the device can keep resident at once for the pair kernel.
+template <int BN>
+int pair_clusters() {
+  static int n = -1;
+  if (n < 0) {
+    cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         PairCfg<BN>::SMEM_BYTES);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * num_sms());
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = PairCfg<BN>::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int c = 0;
+    if (cudaOccupancyMaxActiveClusters(&c, gemm_tcgen05_pair_kernel<BN>, &cfg) != cudaSuccess || c <= 0) {
+      cudaGetLastError();
+      c = 0;
+    }
+    if (getenv("LT_GEMM_DEBUG")) fprintf(stderr, "pair_clusters<%d> = %d\n", BN, c);
+    n = c;
+  }
+  return n;
+}
+
+template <int BN>
+cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
+  using Cfg = PairCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int clusters = pair_clusters<BN>();
+  if (clusters <= 0) return cudaErrorNotSupported;
+  KernelParams p = make_params(a);
+  p.tiles_m = (a.M + 2 * BM - 1) / (2 * BM);
+  p.tiles_n = (a.N + BN - 1) / BN;
+  CUtensorMap ta, tb;
+  const uint64_t nbi = p.batch_inner, nbo = p.batch_total / p.batch_inner;
+  bool ok;
+  if (!a.a_mn_major)
+    ok = encode_operand_map(&ta, a.A, a.K, a.M, nbi, nbo, a.lda, a.a_stride_inner,
+                            a.a_stride_outer, BK, BM);
+  else
+    ok = encode_operand_map(&ta, a.A, a.M, a.K, nbi, nbo, a.lda, a.a_stride_inner,
+                            a.a_stride_outer, 64, BK);
+  if (!a.b_mn_major)
+    ok = ok && encode_operand_map(&tb, a.B, a.K, a.N, nbi, nbo, a.ldb, a.b_stride_inner,
+                                  a.b_stride_outer, BK, Cfg::B_ROWS);
+  else
+    ok = ok && encode_operand_map(&tb, a.B, a.N, a.K, nbi, nbo, a.ldb, a.b_stride_inner,
+                                  a.b_stride_outer, 64, BK);
+  if (!ok) return cudaErrorInvalidValue;
+  const long long total = (long long)p.tiles_m * p.tiles_n * p.batch_total;
+  const int grid = 2 * (int)(total < clusters ? total : clusters);
+  gemm_tcgen05_pair_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+// 0 = single-CTA kernels only, 1 = CTA pairs where the shape allows (default); the
+// LT_GEMM_PAIR environment variable overrides, LT_GEMM_BN forces a tile width (tuning aids).
+int pair_mode() {
+  static int m = -1;
+  if (m < 0) {
+    const char* e = getenv("LT_GEMM_PAIR");
+    m = e ? atoi(e) : 1;
+  }
+  return m;
+}
+int forced_bn() {
+  static int m = -1;
+  if (m < 0) {
+    const char* e = getenv("LT_GEMM_BN");
+    m = e ? atoi(e) : 0;
+  }
+  return m;
+}
+
 cudaError_t launch_simt(const GemmArgs& a, cudaStream_t stream) {
   KernelParams p = make_params(a);
   p.vec_ok = 0;
@@ -705,25 +1026,61 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0) return cudaSuccess;
   if (a.K <= 0) return cudaErrorInvalidValue;
   if (!gemm_uses_tensor_cores(a)) return launch_simt(a, stream);
-  // Tile width: prefer 256-wide tiles when they fill the machine, otherwise 128.
   const long long batch = (long long)(a.batch_inner < 1 ? 1 : a.batch_inner) *
                           (a.batch_outer < 1 ? 1 : a.batch_outer);
-  const long long tm = (a.M + BM - 1) / BM;
   const int sms = num_sms();
-  // Candidate tile widths; score = wave-quantisation efficiency x a mild preference for wide
-  // tiles (each A tile is reused across more columns, and fewer epilogues per FLOP).
-  const int widths[4] = {256, 192, 128, 64};
-  const double pref[4] = {1.00, 0.97, 0.92, 0.80};
-  int best = 128;
-  double best_score = -1.0;
-  for (int i = 0; i < 4; ++i) {
-    const int bn = widths[i];
+  // Candidates: CTA-pair tiles (256 x BN over two SMs) and single-CTA tiles (128 x BN).  Each is
+  // costed with a small model fitted to measurements on B200: a tile takes the longest of
+  //   its MMAs        (K/16 instructions of BN/2 cycles),
+  //   its operand feed (every resident CTA pulls (128 + its B rows) x K bf16 through L2; the
+  //                     L2 -> SM fabric sustains about 12.5 TB/s over the whole chip),
+  //   its epilogue     (128 x BN outputs per CTA, about 3 TB/s of stores over the chip),
+  // tiles run in waves over the resident CTAs / CTA pairs, and a launch costs a fixed few
+  // microseconds (more for cluster launches).
+  struct Cand { int pair, bn; };
+  const Cand cands[7] = {{1, 256}, {1, 192}, {1, 128}, {0, 256}, {0, 192}, {0, 128}, {0, 64}};
+  const bool pair_ok = pair_mode() != 0 && a.causal_tiles == 0 && a.M > BM;
+  const int force = forced_bn();
+  const int clusters = pair_ok ? pair_clusters<256>() : 0;
+  int best_pair = 0, best = 128;
+  double best_cost = 1e30;
+  for (int i = 0; i < 7; ++i) {
+    const Cand& c = cands[i];
+    const int bn = c.bn;
+    if (force && bn != force) continue;
+    if (c.pair) {
+      if (clusters <= 0) continue;
+      if (a.b_mn_major && (bn / 2) % 64 != 0) continue;   // MN-major B arrives in 64-column chunks
+    }
     if (bn > 64 && a.N <= bn / 2) continue;
-    const long long tiles = tm * ((a.N + bn - 1) / bn) * batch;
-    const long long waves = (tiles + sms - 1) / sms;
-    const double useful = (double)a.N / (double)(((a.N + bn - 1) / bn) * bn);
-    const double score = (double)tiles / (double)(waves * sms) * useful * pref[i];
-    if (score > best_score) { best_score = score; best = bn; }
+    const int rows = c.pair ? 2 * BM : BM;
+    const long long units = c.pair ? clusters : sms;
+    const long long tiles = ((a.M + rows - 1) / rows) * ((a.N + bn - 1) / bn) * batch;
+    const double ctas = (double)(c.pair ? 2 * units : units);
+    const double kd = (double)((a.K + BK - 1) / BK * BK);
+    const double t_mma = kd / 16.0 * (bn / 2.0) / 1.7e9;
+    const double b_rows = c.pair ? bn / 2.0 : (double)bn;
+    // time of one wave in which a fraction `f` of the chip is busy
+    auto wave_time = [&](double f) {
+      const double t_feed = ctas * f * (128.0 + b_rows) * kd * 2.0 / 12.5e12;
+      const double t_epi = ctas * f * 128.0 * bn * (a.c_fp32 ? 4.0 : 2.0) / 3.0e12;
+      double t = t_mma > t_feed ? t_mma : t_feed;
+      return t_epi > t ? t_epi : t;
+    };
+    const long long full = tiles / units, rem = tiles % units;
+    const double cost = (c.pair ? 8.5e-6 : 5.5e-6) + (double)full * wave_time(1.0) +
+                        (rem ? wave_time((double)rem / (double)units) : 0.0);
+    if (cost < best_cost) { best_cost = cost; best = bn; best_pair = c.pair; }
+  }
+  if (getenv("LT_GEMM_DEBUG"))
+    fprintf(stderr, "gemm %dx%dx%d batch %lld -> %s BN=%d (model %.1f us)\n", a.M, a.N, a.K, batch,
+            best_pair ? "pair" : "single", best, best_cost * 1e6);
+  if (best_pair) {
+    switch (best) {
+      case 256: return launch_pair<256>(a, stream);
+      case 192: return launch_pair<192>(a, stream);
+      default: return launch_pair<128>(a, stream);
+    }
   }
   switch (best) {
     case 256: return launch_tc<256>(a, stream);
