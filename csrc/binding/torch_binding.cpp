@@ -108,6 +108,14 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, int64_t M, int64_t N, int
   if (aux_out.has_value()) g.aux_out = aux_out->data_ptr();
   if (aux_in.has_value()) { g.aux_in = aux_in->data_ptr(); g.ld_aux = ld_aux; }
   g.causal_tiles = (int)causal_tiles;
+  // scratch for split-K comes from torch's caching allocator, so it is stream-ordered
+  Tensor ws;
+  const size_t ws_bytes = lt::gemm_split_k_workspace_bytes(g);
+  if (ws_bytes) {
+    ws = torch::empty({(int64_t)(ws_bytes / 4)}, C.options().dtype(torch::kFloat32));
+    g.workspace = ws.data_ptr();
+    g.workspace_bytes = ws_bytes;
+  }
   check(lt::gemm_bf16(g, cur_stream()), "gemm");
 }
 

@@ -52,7 +52,16 @@ struct GemmArgs {
   int64_t ld_aux = 0;
   int causal_tiles = 0;  // 1: skip output tiles strictly above the diagonal (n0 > m0 + BM - 1);
                          // 2: skip tiles strictly below (m0 > n0 + BN - 1)
+  // Optional scratch for split-K (fp32, device memory valid on `stream`).  When a long-K
+  // product has too few output tiles to fill the chip (weight gradients: K = tokens), K is cut
+  // into S slices that run as S batches into workspace[S][M][N], and a second kernel sums the
+  // slices in fixed order (deterministic) into C.  Without a workspace no split is made.
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
 };
+
+// Bytes of workspace with which `args` would use split-K (0: it would not split).
+size_t gemm_split_k_workspace_bytes(const GemmArgs& args);
 
 // Returns cudaSuccess or the launch error. Uses the tensor-core path whenever the
 // operands satisfy TMA alignment (base 16 B aligned, lda/ldb multiples of 8

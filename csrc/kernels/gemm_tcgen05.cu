@@ -38,13 +38,22 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int EPI_WARPS = LT_EPI_WARPS;     // EPI_WARPS/4 warps per TMEM lane quadrant share the columns
 constexpr int EPI_SPLIT = EPI_WARPS / 4;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
-constexpr int SMEM_BUDGET = 200 * 1024;
+#ifndef LT_SMEM_BUDGET_KB
+#define LT_SMEM_BUDGET_KB 200
+#endif
+constexpr int SMEM_BUDGET = LT_SMEM_BUDGET_KB * 1024;   // operand ring per CTA
 
+// A pipeline stage holds KSUB 64-wide k blocks of both operands: one barrier round trip then
+// covers KSUB x 4 MMAs.  (Measured: a stage costs about 0.17 us of hand-off on top of its
+// bytes, so narrow tiles, whose stages are small, gain from two blocks per stage.)
 template <int BN>
 struct TileCfg {
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;   // 4 at BN=256, 6 at BN=128
+  static constexpr int KSUB = BN <= 128 ? 2 : 1;
+  static constexpr int B_SUB_BYTES = BN * BK * 2;
+  static constexpr int A_STAGE = A_STAGE_BYTES * KSUB;
+  static constexpr int B_STAGE_BYTES = B_SUB_BYTES * KSUB;
+  static constexpr int STAGE_BYTES = A_STAGE + B_STAGE_BYTES;
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;   // 4 at BN=256 and at BN=128
   static constexpr int TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);  // power of two
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -324,7 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+  uint8_t* smem_b = smem + STAGES * Cfg::A_STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
   uint64_t* full_bar = bars;                    // [STAGES]
   uint64_t* empty_bar = bars + STAGES;          // [STAGES]
@@ -359,7 +368,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_holder;
 
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb = (p.K + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int total_tiles = tiles_per_batch * p.batch_total;
 
@@ -390,22 +399,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           const uint32_t fb = smem_u32(&full_bar[stage]);
           mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
-          const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
-          const uint32_t sb = smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES);
-          const int k0 = kb * BK;
-          if (!p.a_mn) {
-            tma_load_4d(sa, &tmap_a, fb, k0, m0, bi, bo);
-          } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c)
-              tma_load_4d(sa + c * (64 * BK * 2), &tmap_a, fb, m0 + 64 * c, k0, bi, bo);
-          }
-          if (!p.b_mn) {
-            tma_load_4d(sb, &tmap_b, fb, k0, n0, bi, bo);
-          } else {
+          for (int sub = 0; sub < Cfg::KSUB; ++sub) {
+            const uint32_t sa = smem_u32(smem_a + stage * Cfg::A_STAGE + sub * A_STAGE_BYTES);
+            const uint32_t sb = smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES + sub * Cfg::B_SUB_BYTES);
+            const int k0 = (kb * Cfg::KSUB + sub) * BK;   // past K: the load returns zeros
+            if (!p.a_mn) {
+              tma_load_4d(sa, &tmap_a, fb, k0, m0, bi, bo);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_4d(sb + c * (64 * BK * 2), &tmap_b, fb, n0 + 64 * c, k0, bi, bo);
+              for (int c = 0; c < BM / 64; ++c)
+                tma_load_4d(sa + c * (64 * BK * 2), &tmap_a, fb, m0 + 64 * c, k0, bi, bo);
+            }
+            if (!p.b_mn) {
+              tma_load_4d(sb, &tmap_b, fb, k0, n0, bi, bo);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                tma_load_4d(sb + c * (64 * BK * 2), &tmap_b, fb, n0 + 64 * c, k0, bi, bo);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -451,14 +463,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           tc_fence_after_sync();
-          const uint64_t a_desc = make_smem_desc_sw128(
-              smem_u32(smem_a + stage * A_STAGE_BYTES), a_lbo, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(
-              smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES), b_lbo, 1024);
 #pragma unroll
-          for (int j = 0; j < BK / UMMA_K; ++j) {
-            umma_bf16(d_tmem, a_desc + (uint64_t)(j * a_step), b_desc + (uint64_t)(j * b_step),
-                      idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          for (int sub = 0; sub < Cfg::KSUB; ++sub) {
+            const uint64_t a_desc = make_smem_desc_sw128(
+                smem_u32(smem_a + stage * Cfg::A_STAGE + sub * A_STAGE_BYTES), a_lbo, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(
+                smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES + sub * Cfg::B_SUB_BYTES), b_lbo, 1024);
+#pragma unroll
+            for (int j = 0; j < BK / UMMA_K; ++j) {
+              umma_bf16(d_tmem, a_desc + (uint64_t)(j * a_step), b_desc + (uint64_t)(j * b_step),
+                        idesc, (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
+            }
           }
           umma_commit(smem_u32(&empty_bar[stage]));  // frees the smem stage when MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -517,7 +532,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 //   tmem_full (both CTAs) / tmem_empty (even CTA, one arrive per epilogue warp of both CTAs).
 // ------------------------------------------------------------------------------
 #ifndef LT_PAIR_KSUB
-#define LT_PAIR_KSUB 1
+#define LT_PAIR_KSUB 2
 #endif
 template <int BN>
 struct PairCfg {
@@ -527,7 +542,7 @@ struct PairCfg {
   static constexpr int A_STAGE = A_STAGE_BYTES * KSUB;
   static constexpr int B_STAGE_BYTES = B_SUB_BYTES * KSUB;
   static constexpr int STAGE_BYTES = A_STAGE + B_STAGE_BYTES;
-  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;  // 6 at BN=256, 8 at BN=128 (KSUB 1)
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;  // 3 at BN=256, 4 at BN=128
   static constexpr int TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
@@ -1022,28 +1037,27 @@ bool gemm_uses_tensor_cores(const GemmArgs& a) {
   return true;
 }
 
-cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
-  if (a.M <= 0 || a.N <= 0) return cudaSuccess;
-  if (a.K <= 0) return cudaErrorInvalidValue;
-  if (!gemm_uses_tensor_cores(a)) return launch_simt(a, stream);
-  const long long batch = (long long)(a.batch_inner < 1 ? 1 : a.batch_inner) *
-                          (a.batch_outer < 1 ? 1 : a.batch_outer);
-  const int sms = num_sms();
-  // Candidates: CTA-pair tiles (256 x BN over two SMs) and single-CTA tiles (128 x BN).  Each is
-  // costed with a small model fitted to measurements on B200: a tile takes the longest of
-  //   its MMAs        (K/16 instructions of BN/2 cycles),
-  //   its operand feed (every resident CTA pulls (128 + its B rows) x K bf16 through L2; the
-  //                     L2 -> SM fabric sustains about 12.5 TB/s over the whole chip),
-  //   its epilogue     (128 x BN outputs per CTA, about 3 TB/s of stores over the chip),
-  // tiles run in waves over the resident CTAs / CTA pairs, and a launch costs a fixed few
-  // microseconds (more for cluster launches).
+namespace {
+
+struct TileChoice { int pair = 0, bn = 128; double cost = 1e30; };
+
+// Candidates: CTA-pair tiles (256 x BN over two SMs) and single-CTA tiles (128 x BN).  Each is
+// costed with a small model fitted to measurements on B200: a tile takes the longest of
+//   its pipeline stages (per stage the slower of the MMAs, BN/2 cycles each, and the operand
+//                     feed: about 0.17 us of barrier hand-off plus the bytes at the ~140 GB/s one
+//                     SM pulls through TMA),
+//   the chip-wide L2 -> SM traffic of the wave at about 12.5 TB/s,
+//   its epilogue     (128 x BN outputs per CTA, about 3 TB/s of stores over the chip),
+// tiles run in waves over the resident CTAs / CTA pairs, and a launch costs a fixed few
+// microseconds (more for cluster launches).
+TileChoice choose_tile(const GemmArgs& a, int K, long long batch, bool c_fp32) {
   struct Cand { int pair, bn; };
   const Cand cands[7] = {{1, 256}, {1, 192}, {1, 128}, {0, 256}, {0, 192}, {0, 128}, {0, 64}};
+  const int sms = num_sms();
   const bool pair_ok = pair_mode() != 0 && a.causal_tiles == 0 && a.M > BM;
   const int force = forced_bn();
   const int clusters = pair_ok ? pair_clusters<256>() : 0;
-  int best_pair = 0, best = 128;
-  double best_cost = 1e30;
+  TileChoice best;
   for (int i = 0; i < 7; ++i) {
     const Cand& c = cands[i];
     const int bn = c.bn;
@@ -1057,37 +1071,154 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     const long long units = c.pair ? clusters : sms;
     const long long tiles = ((a.M + rows - 1) / rows) * ((a.N + bn - 1) / bn) * batch;
     const double ctas = (double)(c.pair ? 2 * units : units);
-    const double kd = (double)((a.K + BK - 1) / BK * BK);
-    const double t_mma = kd / 16.0 * (bn / 2.0) / 1.7e9;
+    const int ksub = c.pair ? PairCfg<256>::KSUB : (bn <= 128 ? 2 : 1);
+    const double stages = (double)((K + BK * ksub - 1) / (BK * ksub));
     const double b_rows = c.pair ? bn / 2.0 : (double)bn;
+    const double stage_bytes = ksub * (128.0 + b_rows) * BK * 2.0;
+    // per stage: the MMAs, or the hand-off plus the bytes at what one SM pulls through TMA
+    const double s_mma = ksub * 4.0 * (bn / 2.0) / 1.7e9 * 1.1;
+    const double s_feed = 0.175e-6 + stage_bytes / 142.0e9;
+    const double t_cta = stages * (s_mma > s_feed ? s_mma : s_feed) + 0.4e-6;
     // time of one wave in which a fraction `f` of the chip is busy
     auto wave_time = [&](double f) {
-      const double t_feed = ctas * f * (128.0 + b_rows) * kd * 2.0 / 12.5e12;
-      const double t_epi = ctas * f * 128.0 * bn * (a.c_fp32 ? 4.0 : 2.0) / 3.0e12;
-      double t = t_mma > t_feed ? t_mma : t_feed;
+      const double t_l2 = ctas * f * stages * stage_bytes / 12.5e12;
+      const double t_epi = ctas * f * 128.0 * bn * (c_fp32 ? 4.0 : 2.0) / 3.0e12;
+      double t = t_cta > t_l2 ? t_cta : t_l2;
       return t_epi > t ? t_epi : t;
     };
     const long long full = tiles / units, rem = tiles % units;
     const double cost = (c.pair ? 8.5e-6 : 5.5e-6) + (double)full * wave_time(1.0) +
                         (rem ? wave_time((double)rem / (double)units) : 0.0);
-    if (cost < best_cost) { best_cost = cost; best = bn; best_pair = c.pair; }
+    if (cost < best.cost) { best.cost = cost; best.bn = bn; best.pair = c.pair; }
   }
-  if (getenv("LT_GEMM_DEBUG"))
-    fprintf(stderr, "gemm %dx%dx%d batch %lld -> %s BN=%d (model %.1f us)\n", a.M, a.N, a.K, batch,
-            best_pair ? "pair" : "single", best, best_cost * 1e6);
-  if (best_pair) {
-    switch (best) {
+  return best;
+}
+
+// Split-K factor for `a` (1 = none) and the tile to use for the slices.
+int choose_split(const GemmArgs& a, TileChoice* slice_tile) {
+  const long long batch = (long long)(a.batch_inner < 1 ? 1 : a.batch_inner) *
+                          (a.batch_outer < 1 ? 1 : a.batch_outer);
+  TileChoice whole = choose_tile(a, a.K, batch, a.c_fp32 != 0);
+  *slice_tile = whole;
+  if (batch != 1 || a.bias || a.act != GEMM_ACT_NONE || a.residual || a.aux_out || a.aux_in ||
+      a.causal_tiles || a.K < 2048 || getenv("LT_GEMM_NO_SPLIT"))
+    return 1;
+  int best_s = 1;
+  double best_cost = whole.cost;
+  const int splits[7] = {2, 3, 4, 6, 8, 12, 16};
+  for (int i = 0; i < 7; ++i) {
+    const int s = splits[i];
+    if (a.K % (s * BK) != 0 || a.K / s < 8 * BK) continue;
+    TileChoice t = choose_tile(a, a.K / s, s, true);
+    // the second pass reads S fp32 slices and writes C; it mostly hits in L2
+    const double reduce = 4.0e-6 + ((double)s * 4.0 + 4.0) * (double)a.M * (double)a.N / 4.0e12;
+    const double cost = t.cost + reduce;
+    if (cost < best_cost * 0.9) { best_cost = cost; best_s = s; *slice_tile = t; }
+  }
+  return best_s;
+}
+
+cudaError_t launch_choice(const TileChoice& t, const GemmArgs& a, cudaStream_t stream) {
+  if (t.pair) {
+    switch (t.bn) {
       case 256: return launch_pair<256>(a, stream);
       case 192: return launch_pair<192>(a, stream);
       default: return launch_pair<128>(a, stream);
     }
   }
-  switch (best) {
+  switch (t.bn) {
     case 256: return launch_tc<256>(a, stream);
     case 192: return launch_tc<192>(a, stream);
     case 64: return launch_tc<64>(a, stream);
     default: return launch_tc<128>(a, stream);
   }
+}
+
+// C = sum_s ws[s] (+ C), four elements per thread; slices are added in index order.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slice, int M, int N,
+                     void* C, long long ldc, int c_fp32, int accumulate) {
+  const long long quads = (long long)M * (N / 4);
+  for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < quads;
+       q += (long long)gridDim.x * blockDim.x) {
+    const long long row = q / (N / 4);
+    const int col = (int)(q - row * (N / 4)) * 4;
+    const float* src = ws + row * N + col;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + s * slice);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (c_fp32) {
+      float4* dst = reinterpret_cast<float4*>((float*)C + row * ldc + col);
+      if (accumulate) { const float4 o = *dst; acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w; }
+      *dst = acc;
+    } else {
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)C + row * ldc + col);
+      if (accumulate) {
+        const float2 o0 = __bfloat1622float2(dst[0]), o1 = __bfloat1622float2(dst[1]);
+        acc.x += o0.x; acc.y += o0.y; acc.z += o1.x; acc.w += o1.y;
+      }
+      dst[0] = __floats2bfloat162_rn(acc.x, acc.y);
+      dst[1] = __floats2bfloat162_rn(acc.z, acc.w);
+    }
+  }
+}
+
+bool split_k_shape_ok(const GemmArgs& a) {
+  return a.N % 4 == 0 && a.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(a.C) & 15) == 0;
+}
+
+}  // namespace
+
+size_t gemm_split_k_workspace_bytes(const GemmArgs& a) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || !gemm_uses_tensor_cores(a) || !split_k_shape_ok(a)) return 0;
+  TileChoice t;
+  const int s = choose_split(a, &t);
+  return s > 1 ? (size_t)s * (size_t)a.M * (size_t)a.N * sizeof(float) : 0;
+}
+
+cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return cudaSuccess;
+  if (a.K <= 0) return cudaErrorInvalidValue;
+  if (!gemm_uses_tensor_cores(a)) return launch_simt(a, stream);
+  TileChoice tile;
+  int splits = choose_split(a, &tile);
+  const size_t need = (size_t)splits * (size_t)a.M * (size_t)a.N * sizeof(float);
+  if (splits > 1 && (!a.workspace || a.workspace_bytes < need || !split_k_shape_ok(a))) {
+    splits = 1;
+    tile = choose_tile(a, a.K, 1, a.c_fp32 != 0);
+  }
+  if (getenv("LT_GEMM_DEBUG"))
+    fprintf(stderr, "gemm %dx%dx%d -> %s BN=%d split %d (model %.1f us)\n", a.M, a.N, a.K,
+            tile.pair ? "pair" : "single", tile.bn, splits, tile.cost * 1e6);
+  if (splits == 1) return launch_choice(tile, a, stream);
+  // K slices as batches into the fp32 workspace, then one deterministic reduction
+  GemmArgs g = a;
+  const int ks = a.K / splits;
+  g.K = ks;
+  g.batch_inner = splits;
+  g.batch_outer = 1;
+  g.a_stride_inner = a.a_mn_major ? (int64_t)ks * a.lda : ks;
+  g.b_stride_inner = a.b_mn_major ? (int64_t)ks * a.ldb : ks;
+  g.a_stride_outer = g.b_stride_outer = 0;
+  g.C = a.workspace;
+  g.ldc = a.N;
+  g.c_stride_inner = (int64_t)a.M * a.N;
+  g.c_stride_outer = 0;
+  g.c_fp32 = 1;
+  g.accumulate = 0;
+  g.workspace = nullptr;
+  cudaError_t e = launch_choice(tile, g, stream);
+  if (e != cudaSuccess) return e;
+  const long long quads = (long long)a.M * (a.N / 4);
+  int blocks = (int)((quads + 255) / 256);
+  if (blocks > 8 * num_sms()) blocks = 8 * num_sms();
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>((const float*)a.workspace, splits,
+                                                   (long long)a.M * a.N, a.M, a.N, a.C, a.ldc,
+                                                   a.c_fp32, a.accumulate);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
 }
 
 int gemm_last_device_error() {

@@ -76,6 +76,29 @@ def test_gemm_epilogues(C):
     torch.testing.assert_close(c, 0.5 * base + 1.0, atol=0.02, rtol=0.01)
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(768, 768, 8192, True, True), (768, 2304, 4096, True, True),
+                                             (384, 512, 4096, False, True)])
+def test_gemm_split_k(C, M, N, K, a_mn, b_mn):
+    """Long-K, few-tile products (weight gradients) run as K slices + a fixed-order reduction."""
+    torch.manual_seed(3)
+    A = torch.randn(M, K, device="cuda") * 0.1
+    B = torch.randn(K, N, device="cuda") * 0.1
+    a = (A.t().contiguous() if a_mn else A).bfloat16()
+    b = (B if b_mn else B.t().contiguous()).bfloat16()
+    ref = A.bfloat16().float() @ B.bfloat16().float()
+    out = _gemm(C, a, b, M, N, K, a_mn, b_mn).float()
+    torch.testing.assert_close(out, ref, atol=0.05, rtol=0.02)
+    # accumulate into an existing bf16 gradient, twice: results must be bit-identical
+    g1 = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    g2 = g1.clone()
+    for g in (g1, g2):
+        C.gemm(a, b, g, M, N, K, a.stride(0), b.stride(0), N, a_mn, b_mn, 1, 1, 0, 0, 0, 0, 0, 0,
+               1.0, True, None, 0, None, 0, None, None, 0, 0)
+    torch.testing.assert_close(g1.float(), ref + 1.0, atol=0.06, rtol=0.02)
+    assert torch.equal(g1, g2)
+    assert C.gemm_device_error() == 0
+
+
 def test_gemm_simt_fallback_and_batched(C):
     torch.manual_seed(2)
     a = torch.randn(64, 256, device="cuda").bfloat16()
