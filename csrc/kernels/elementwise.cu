@@ -273,6 +273,73 @@ __global__ void colsum_stage2(const float* __restrict__ scratch, int64_t slabs, 
   if (accumulate) t += VecIO<TO>::ld(out + col);
   VecIO<TO>::st(out + col, t);
 }
+
+// Single-launch form for 16-byte-aligned inputs: block = (32 x V columns, slab of rows), eight
+// warps stride over the slab with independent vector loads; the partial row of the slab goes to
+// scratch and the LAST block of a column group (ticket) adds the slabs in index order, so the
+// result does not depend on which block that is.  The ticket words live in this module and are
+// left at zero; calls that can overlap on different streams must not share column groups.
+constexpr int CS_MAX_GROUPS = 1024;
+__device__ unsigned int g_colsum_tickets[CS_MAX_GROUPS];
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+colsum_fused(const T* __restrict__ in, int64_t ld, int64_t rows, int64_t cols,
+             int64_t rows_per_slab, float* __restrict__ scratch, TO* __restrict__ out,
+             int accumulate) {
+  constexpr int V = VecIO<T>::N;
+  __shared__ float sh[8][32 * V + 1];
+  __shared__ int is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c0 = ((int64_t)blockIdx.x * 32 + lane) * V;
+  const bool ok = c0 < cols;
+  const int64_t r0 = blockIdx.y * rows_per_slab;
+  const int64_t r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+  if (ok) {
+#pragma unroll 4
+    for (int64_t r = r0 + warp; r < r1; r += 8) {
+      float v[V];
+      VecIO<T>::load(in + r * ld + c0, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) sh[warp][lane * V + j] = acc[j];
+  __syncthreads();
+  const int64_t gcol0 = (int64_t)blockIdx.x * 32 * V;
+  for (int c = threadIdx.x; c < 32 * V; c += 256) {
+    if (gcol0 + c < cols) {
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += sh[w][c];
+      scratch[(int64_t)blockIdx.y * cols + gcol0 + c] = t;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(&g_colsum_tickets[blockIdx.x], 1u);
+    is_last = (t == gridDim.y - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int c = threadIdx.x; c < 32 * V; c += 256) {
+    const int64_t col = gcol0 + c;
+    if (col < cols) {
+      float t = 0.0f;
+      for (unsigned int sidx = 0; sidx < gridDim.y; ++sidx)
+        t += __ldcg(scratch + (int64_t)sidx * cols + col);
+      if (accumulate) t += VecIO<TO>::ld(out + col);
+      VecIO<TO>::st(out + col, t);
+    }
+  }
+  if (threadIdx.x == 0) g_colsum_tickets[blockIdx.x] = 0;
+}
 }  // namespace
 
 int64_t column_sum_scratch_floats(int64_t rows, int64_t cols) {
@@ -283,6 +350,29 @@ cudaError_t column_sum(int dtype, const void* in, int64_t ld, void* out, int out
                        int accumulate, int64_t rows, int64_t cols, float* scratch,
                        cudaStream_t s) {
   if (cols <= 0) return cudaSuccess;
+  {
+    const int v = dtype == DT_F32 ? 4 : 8;
+    const int64_t groups = (cols + 32 * v - 1) / (32 * v);
+    if (rows > 0 && cols % v == 0 && ld % v == 0 && is_aligned16(in) && groups <= CS_MAX_GROUPS) {
+      // about four blocks per SM, and never more slabs than the scratch was sized for
+      int64_t slabs = (4 * 148 + groups - 1) / groups;
+      const int64_t max_slabs = (rows + CS_ROWS - 1) / CS_ROWS;
+      if (slabs > max_slabs) slabs = max_slabs;
+      if (slabs > 64) slabs = 64;   // the closing block adds the slabs one after another
+      if (slabs < 1) slabs = 1;
+      const int64_t rps = (rows + slabs - 1) / slabs;
+      slabs = (rows + rps - 1) / rps;
+      dim3 g((unsigned)groups, (unsigned)slabs);
+      LT_DISPATCH_DTYPE(dtype, T, {
+        LT_DISPATCH_DTYPE(out_dtype, TO, {
+          colsum_fused<T, TO><<<g, 256, 0, s>>>((const T*)in, ld, rows, cols, rps, scratch,
+                                                (TO*)out, accumulate);
+          LT_COUNT_LAUNCH();
+          return cudaGetLastError();
+        })
+      })
+    }
+  }
   const int64_t slabs = (rows + CS_ROWS - 1) / CS_ROWS;
   dim3 g1((unsigned)((cols + 31) / 32), (unsigned)(slabs > 0 ? slabs : 1));
   LT_DISPATCH_DTYPE(dtype, T, {

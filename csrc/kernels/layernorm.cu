@@ -102,46 +102,42 @@ ln_fwd_generic(const T* __restrict__ x, const TP* __restrict__ gamma, const TP* 
 }
 
 // ----------------------------------------------------------------------------- backward
+// dx: one warp per row, the row's x and dy stay in registers between the two passes; no
+// per-column state, so many warps are resident and enough loads are in flight to fill HBM.
 template <typename T, typename TP, int NV>
 __global__ void __launch_bounds__(THREADS)
-ln_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
-              const float* __restrict__ mean, const float* __restrict__ rstd,
-              const T* __restrict__ dx_add, T* __restrict__ dx, float* __restrict__ scratch,
-              int64_t rows, int64_t cols) {
+ln_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
+             const float* __restrict__ mean, const float* __restrict__ rstd,
+             const T* __restrict__ dx_add, T* __restrict__ dx, int64_t rows, int64_t cols) {
   constexpr int V = VecIO<T>::N;
-  extern __shared__ float sh_acc[];  // [2][cols]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t nvec = cols / V;
-  float dg[NV][V], db[NV][V], gm[NV][V];
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int64_t vi = lane + 32 * i;
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-      dg[i][j] = 0.0f; db[i][j] = 0.0f;
-      gm[i][j] = vi < nvec ? ldp(gamma, vi * V + j) : 0.0f;
-    }
-  }
   for (int64_t row = blockIdx.x * (int64_t)WARPS + warp; row < rows;
        row += (int64_t)gridDim.x * WARPS) {
     const T* xr = x + row * cols;
     const T* dyr = dy + row * cols;
+    float xv[NV][V], g[NV][V], o[NV][V];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t vi = lane + 32 * i;
+      if (vi < nvec) {
+        VecIO<T>::load(xr + vi * V, xv[i]);
+        VecIO<T>::load(dyr + vi * V, g[i]);
+        if (dx_add) VecIO<T>::load(dx_add + row * cols + vi * V, o[i]);
+      }
+    }
     const float mu = mean[row], rs = rstd[row];
     float c1 = 0.0f, c2 = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
-        float xv[V], dv[V];
-        VecIO<T>::load(xr + vi * V, xv);
-        VecIO<T>::load(dyr + vi * V, dv);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float xh = (xv[j] - mu) * rs;
-          const float g = dv[j] * gm[i][j];
-          c1 += g; c2 += g * xh;
-          dg[i][j] += dv[j] * xh;
-          db[i][j] += dv[j];
+          xv[i][j] = (xv[i][j] - mu) * rs;              // x_hat
+          g[i][j] *= ldp(gamma, vi * V + j);            // dy * gamma
+          c1 += g[i][j];
+          c2 += g[i][j] * xv[i][j];
         }
       }
     }
@@ -152,41 +148,67 @@ ln_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __res
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
-        float xv[V], dv[V], o[V];
-        VecIO<T>::load(xr + vi * V, xv);   // second touch comes from L1 / L2
-        VecIO<T>::load(dyr + vi * V, dv);
-        if (dx_add) VecIO<T>::load(dx_add + row * cols + vi * V, o);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float xh = (xv[j] - mu) * rs;
-          const float r = rs * (dv[j] * gm[i][j] - c1 - xh * c2);
-          o[j] = dx_add ? o[j] + r : r;
+          const float r = rs * (g[i][j] - c1 - xv[i][j] * c2);
+          o[i][j] = dx_add ? o[i][j] + r : r;
         }
-        VecIO<T>::store(dxr + vi * V, o);
+        VecIO<T>::store(dxr + vi * V, o[i]);
       }
     }
   }
-  // fold the eight warps of this block in a fixed order
-  for (int c = threadIdx.x; c < 2 * cols; c += THREADS) sh_acc[c] = 0.0f;
+}
+
+// dgamma / dbeta partial sums: block (column group of 32 x V columns, slab of rows); the
+// eight warps stride over the slab's rows with independent loads (x and dy were just read by
+// the dx kernel, so they mostly come from L2) and are folded in warp order, so the result
+// does not depend on timing.  scratch[slab][0:cols] = sum dy * x_hat, [cols:2 cols] = sum dy.
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+ln_stats_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ mean,
+                const float* __restrict__ rstd, float* __restrict__ scratch, int64_t rows,
+                int64_t cols, int64_t rows_per_slab) {
+  constexpr int V = VecIO<T>::N;
+  __shared__ float sh[WARPS][2][32 * V + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t vi = blockIdx.x * 32 + lane;
+  const bool ok = vi < cols / V;
+  const int64_t r0 = blockIdx.y * rows_per_slab;
+  const int64_t r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+  float dg[V], db[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) { dg[j] = 0.0f; db[j] = 0.0f; }
+  if (ok) {
+#pragma unroll 4
+    for (int64_t row = r0 + warp; row < r1; row += WARPS) {
+      float xv[V], dv[V];
+      VecIO<T>::load(x + row * cols + vi * V, xv);
+      VecIO<T>::load(dy + row * cols + vi * V, dv);
+      const float mu = mean[row], rs = rstd[row];
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        dg[j] += dv[j] * ((xv[j] - mu) * rs);
+        db[j] += dv[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    sh[warp][0][lane * V + j] = dg[j];
+    sh[warp][1][lane * V + j] = db[j];
+  }
   __syncthreads();
-  for (int w = 0; w < WARPS; ++w) {
-    if (warp == w) {
+  float* out = scratch + (int64_t)blockIdx.y * 2 * cols;
+  for (int c = threadIdx.x; c < 2 * 32 * V; c += THREADS) {
+    const int which = c / (32 * V), cc = c - which * 32 * V;
+    const int64_t col = blockIdx.x * 32 * V + cc;
+    if (col < cols) {
+      float acc = 0.0f;
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int64_t vi = lane + 32 * i;
-        if (vi < nvec) {
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            sh_acc[vi * V + j] += dg[i][j];
-            sh_acc[cols + vi * V + j] += db[i][j];
-          }
-        }
-      }
+      for (int w = 0; w < WARPS; ++w) acc += sh[w][which][cc];
+      out[which * cols + col] = acc;
     }
-    __syncthreads();
   }
-  float* out = scratch + (int64_t)blockIdx.x * 2 * cols;
-  for (int c = threadIdx.x; c < 2 * cols; c += THREADS) out[c] = sh_acc[c];
 }
 
 template <typename T, typename TP>
@@ -298,13 +320,11 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
   const bool fast = cols % V == 0 && cols <= 32 * 8 * V && is_aligned16(x) && is_aligned16(dy) &&
                     is_aligned16(dx) && (!dx_add || is_aligned16(dx_add));
   if (fast) {
-    const int grid = bwd_blocks(rows);
-    *nparts = grid;
-    const size_t smem = 2 * cols * sizeof(float);
-#define LT_LN_BWD(NVV)                                                                    \
-  ln_bwd_kernel<T, TP, NVV><<<grid, THREADS, smem, s>>>(                                   \
-      (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx,   \
-      scratch, rows, cols)
+    const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
+#define LT_LN_BWD(NVV)                                                                       \
+  ln_dx_kernel<T, TP, NVV><<<grid, THREADS, 0, s>>>((const T*)x, (const T*)dy,               \
+                                                    (const TP*)gamma, mean, rstd,            \
+                                                    (const T*)dx_add, (T*)dx, rows, cols)
     const int64_t per_lane = (cols / V + 31) / 32;
     if (per_lane <= 1) LT_LN_BWD(1);
     else if (per_lane <= 2) LT_LN_BWD(2);
@@ -312,6 +332,18 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
     else if (per_lane <= 4) LT_LN_BWD(4);
     else LT_LN_BWD(8);
 #undef LT_LN_BWD
+    LT_COUNT_LAUNCH();
+    const int colgroups = (int)((cols / V + 31) / 32);
+    int slabs = 4 * 148 / colgroups;
+    if (slabs > BWD_MAX_BLOCKS) slabs = BWD_MAX_BLOCKS;
+    if (slabs > 96) slabs = 96;   // the parameter reduction walks the slabs one after another
+    if (slabs > bwd_blocks(rows)) slabs = bwd_blocks(rows);
+    if (slabs < 1) slabs = 1;
+    const int64_t rps = (rows + slabs - 1) / slabs;
+    slabs = (int)((rows + rps - 1) / rps);
+    *nparts = slabs;
+    ln_stats_kernel<T><<<dim3((unsigned)colgroups, (unsigned)slabs), THREADS, 0, s>>>(
+        (const T*)x, (const T*)dy, mean, rstd, scratch, rows, cols, rps);
     LT_COUNT_LAUNCH();
   } else {
     ln_bwd_generic<T, TP><<<(unsigned)rows, THREADS, 0, s>>>(
