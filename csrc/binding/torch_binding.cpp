@@ -119,6 +119,41 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, int64_t M, int64_t N, int
   check(lt::gemm_bf16(g, cur_stream()), "gemm");
 }
 
+// C = act(A @ B + bias) where B's row shards live on `world` GPUs and are gathered inside the
+// GEMM kernel (lt::GemmGather).  `b_byte_offset` locates B inside every rank's symmetric buffer;
+// `flags` (world + 1 int32 words) is zeroed here on the launching stream.
+void gemm_gather(const Tensor& A, const Tensor& B_local, Tensor& C, int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ldc, const OptT& bias, int64_t act,
+                 const OptT& aux_out, const Tensor& b_ptrs, const Tensor& signal_ptrs, Tensor& flags,
+                 int64_t rank, int64_t world, int64_t epoch, Tensor& status, bool done_barrier) {
+  TORCH_CHECK(A.is_cuda() && B_local.is_cuda() && C.is_cuda(), "gemm_gather operands must be CUDA tensors");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B_local.scalar_type() == at::kBFloat16 &&
+              C.scalar_type() == at::kBFloat16, "gemm_gather works on bfloat16");
+  TORCH_CHECK(flags.numel() >= world + 1 && flags.scalar_type() == at::kInt, "flags: int32[world+1]");
+  c10::cuda::CUDAGuard guard(A.device());
+  lt::GemmArgs g;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.A = A.data_ptr(); g.B = B_local.data_ptr(); g.C = C.data_ptr();
+  g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+  g.a_mn_major = 0; g.b_mn_major = 1;
+  if (bias.has_value()) {
+    g.bias = bias->data_ptr();
+    g.bias_fp32 = bias->scalar_type() == at::kFloat;
+  }
+  g.act = (int)act;
+  if (aux_out.has_value()) g.aux_out = aux_out->data_ptr();
+  lt::GemmGather gg;
+  gg.b_ptrs = (const uint64_t*)b_ptrs.data_ptr<int64_t>();
+  gg.signal_ptrs = (const uint64_t*)signal_ptrs.data_ptr<int64_t>();
+  gg.flags = (uint32_t*)flags.data_ptr<int>();
+  gg.rank = (int)rank; gg.world = (int)world; gg.epoch = (uint32_t)epoch;
+  gg.status = status.data_ptr<int>();
+  gg.done_barrier = done_barrier ? 1 : 0;
+  g.gather = &gg;
+  check(cudaMemsetAsync(flags.data_ptr(), 0, (size_t)(world + 1) * 4, cur_stream()), "gemm_gather flags");
+  check(lt::gemm_bf16(g, cur_stream()), "gemm_gather");
+}
+
 int64_t gemm_device_error() { return lt::gemm_last_device_error(); }
 
 // ------------------------------------------------------------------------------ elementwise
@@ -605,6 +640,7 @@ std::vector<int64_t> launch_counts() {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_gather", &gemm_gather);
   m.def("gemm_device_error", &gemm_device_error);
   m.def("binary", &binary);
   m.def("scalar", &scalar);

@@ -58,6 +58,30 @@ struct GemmArgs {
   // slices in fixed order (deterministic) into C.  Without a workspace no split is made.
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
+  // Optional: B is sharded by rows over `world` GPUs and gathered INSIDE the kernel
+  // (parameter all-gather fused into the consuming GEMM), see GemmGather.
+  const struct GemmGather* gather = nullptr;
+};
+
+// All-gather of B fused into the GEMM.  Every rank holds a full-size copy of B ([K, N], row
+// stride ldb, b_mn_major = 1) in peer-mapped memory, of which only rows
+// [p K/world, (p+1) K/world) are up to date on rank p.  The kernel
+//   1. tells the peers that the local shard is final and waits (bounded) for theirs,
+//   2. lets the epilogue warps of all CTAs pull the remote shards into the local copy with
+//      16-byte peer loads, in the order (rank+1, rank+2, ...) and counts each finished shard in
+//      `flags`,
+//   3. runs the k loop of every tile starting at the local shard, the TMA producer waiting
+//      (bounded) for a shard's flag only when it first needs rows of that shard,
+// so each remote byte crosses NVLink once and the transfer hides behind the first tiles'
+// math.  After the call the local copy of B is complete.  `flags` must be zero on entry.
+struct GemmGather {
+  const uint64_t* b_ptrs = nullptr;       // device table [world]: every rank's copy of B
+  const uint64_t* signal_ptrs = nullptr;  // device table [world]: signal pads (as in csrc/comm)
+  uint32_t* flags = nullptr;              // local device words [world + 1], zero on entry
+  int rank = 0, world = 1;
+  uint32_t epoch = 0;                     // same on every rank, increases per collective
+  int* status = nullptr;                  // [8] device ints, zero when healthy
+  int done_barrier = 1;                   // wait until every peer has finished copying our shard
 };
 
 // Bytes of workspace with which `args` would use split-K (0: it would not split).

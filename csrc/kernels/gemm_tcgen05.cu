@@ -79,6 +79,14 @@ struct KernelParams {
   int causal_tiles;
   int vec_ok;  // C / residual / aux rows allow 16-byte vector access
   int vec32_ok;  // ... and 32-byte (256-bit) access
+  // all-gather of B fused into the kernel (g_world <= 1: off)
+  const uint64_t* g_b_ptrs;
+  const uint64_t* g_signal_ptrs;
+  uint32_t* g_flags;
+  int* g_status;
+  long long g_ldb;
+  int g_rank, g_world, g_rows_per_shard, g_done;
+  uint32_t g_epoch;
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -520,6 +528,120 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // ------------------------------------------------------------------------------
+// All-gather of B fused into the pair kernel (see GemmGather in gemm.h).
+// ------------------------------------------------------------------------------
+constexpr int GS_START = 0, GS_DONE = 16;        // signal-pad slots, as in csrc/comm/comm_kernels.cu
+constexpr long long GATHER_BUDGET = 6000000000ll;  // about three seconds of SM clocks
+
+__device__ __forceinline__ void g_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t g_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t g_ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 g_ld_peer16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void epi_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+}
+__device__ void g_report(int* status, int code, int rank, uint32_t epoch, int phase, int peer,
+                         uint32_t seen) {
+  if (!status) return;
+  if (atomicCAS(&status[0], 0, code) == 0) {
+    status[1] = rank; status[2] = (int)epoch; status[3] = phase; status[4] = peer;
+    status[5] = (int)seen;
+  }
+}
+// Bounded wait until *flag (signed distance) reaches `target`; acquire at gpu or system scope.
+template <bool SYS>
+__device__ bool g_wait_flag(const uint32_t* flag, uint32_t target, const KernelParams& p, int phase,
+                            int peer) {
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (true) {
+    const uint32_t seen = SYS ? g_ld_acquire_sys(flag) : g_ld_acquire_gpu(flag);
+    if ((int32_t)(seen - target) >= 0) return true;
+    if ((++spins & 0xff) == 0) {
+      if (p.g_status && ((volatile int*)p.g_status)[0] != 0) return false;
+      if (clock64() - t0 > GATHER_BUDGET) {
+        g_report(p.g_status, 2, p.g_rank, p.g_epoch, phase, peer, seen);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
+// Run by the 32 * EPI_WARPS epilogue threads of every CTA before their first tile.
+__device__ void gather_remote_shards(const KernelParams& p, int t, int* sh_fail) {
+  const int W = p.g_world, rank = p.g_rank;
+  if (t == 0) *sh_fail = 0;
+  if (blockIdx.x == 0 && t < W) {
+    __threadfence_system();   // the local shard was written by earlier kernels of this stream
+    g_st_release_sys(reinterpret_cast<uint32_t*>(p.g_signal_ptrs[t]) + GS_START + rank, p.g_epoch);
+  }
+  epi_bar();
+  if (t < W) {
+    const uint32_t* my_pad = reinterpret_cast<const uint32_t*>(p.g_signal_ptrs[rank]);
+    if (!g_wait_flag<true>(my_pad + GS_START + t, p.g_epoch, p, 1, t)) *sh_fail = 1;
+  }
+  epi_bar();
+  const bool failed = *sh_fail != 0;
+  const long long R = p.g_rows_per_shard, nv = p.N / 8;
+  const long long total = R * nv;
+  const long long stride = (long long)gridDim.x * (32 * EPI_WARPS);
+  char* local = reinterpret_cast<char*>(p.g_b_ptrs[rank]);
+  for (int s = 1; s < W; ++s) {
+    const int peer = (rank + s) % W;
+    if (!failed) {
+      const char* src = reinterpret_cast<const char*>(p.g_b_ptrs[peer]);
+      for (long long v0 = (long long)blockIdx.x * (32 * EPI_WARPS) + t; v0 < total; v0 += 4 * stride) {
+        uint4 d[4];
+        long long off[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long v = v0 + u * stride;
+          off[u] = -1;
+          if (v < total) {
+            const long long row = (long long)peer * R + v / nv;
+            off[u] = (row * p.g_ldb + (v % nv) * 8) * 2;
+            d[u] = g_ld_peer16(src + off[u]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (off[u] >= 0) *reinterpret_cast<uint4*>(local + off[u]) = d[u];
+      }
+    }
+    __threadfence();
+    epi_bar();
+    // counted even after a failure, so that no producer waits for a shard in vain (the error
+    // is already recorded in the status words)
+    if (t == 0) atomicAdd(&p.g_flags[peer], 1u);
+  }
+  if (p.g_done && t == 0) {
+    // the last CTA to finish its copies tells every peer that its shard is no longer read
+    const unsigned ticket = atomicAdd(&p.g_flags[W], 1u);
+    if (ticket == gridDim.x - 1) {
+      for (int q = 0; q < W; ++q)
+        g_st_release_sys(reinterpret_cast<uint32_t*>(p.g_signal_ptrs[q]) + GS_DONE + rank, p.g_epoch);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------
 // CTA-pair variant: a cluster of two CTAs (two SMs) owns one 256 x BN output tile.  CTA r holds
 // rows [128 r, 128 r + 128) of the A tile, columns [r BN/2, (r+1) BN/2) of the B tile and the
 // accumulator rows of its half; the even CTA issues tcgen05.mma.cta_group::2 for both.  Each SM
@@ -565,6 +687,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
   uint32_t* tmem_base_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_holder + 1);
+  int* gather_fail = reinterpret_cast<int*>(tmem_base_holder + 2);
 
   const int warp_idx = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -607,13 +730,38 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // fused all-gather: start every tile's k loop at the local shard and wait for a remote
+      // shard only when its rows are first needed
+      const bool gather = p.g_world > 1;
+      const int kb_start = gather ? (p.g_rank * p.g_rows_per_shard) / (BK * Cfg::KSUB) : 0;
+      uint32_t shard_ready = gather ? (1u << p.g_rank) : 0xffffffffu;
       for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
         const int b = tile / tiles_per_batch;
         const int t = tile - b * tiles_per_batch;
         const int m0 = (t % p.tiles_m) * (2 * BM) + (int)cta_rank * BM;
         const int n0 = (t / p.tiles_m) * BN + (int)cta_rank * Cfg::B_ROWS;
         const int bi = b % p.batch_inner, bo = b / p.batch_inner;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kbi = 0; kbi < num_kb; ++kbi) {
+          int kb = kbi + kb_start;
+          if (kb >= num_kb) kb -= num_kb;
+          if (gather) {
+            const int r_lo = kb * Cfg::KSUB * BK, r_hi = r_lo + Cfg::KSUB * BK - 1;
+            int q_lo = r_lo / p.g_rows_per_shard, q_hi = r_hi / p.g_rows_per_shard;
+            if (q_hi > p.g_world - 1) q_hi = p.g_world - 1;
+            bool waited = false;
+            for (int q = q_lo; ok && q <= q_hi; ++q) {
+              if (!((shard_ready >> q) & 1u)) {
+                if (!g_wait_flag<false>(p.g_flags + q, gridDim.x, p, 3, q)) {
+                  *abort_flag = 1;
+                  ok = false;
+                }
+                shard_ready |= 1u << q;
+                waited = true;
+              }
+            }
+            if (!ok) break;
+            if (waited) asm volatile("fence.proxy.async;" ::: "memory");
+          }
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag,
                                  &g_gemm_error, 11)) {
             ok = false;
@@ -712,6 +860,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // -------------------------------- epilogue --------------------------------
     const int quad = warp_idx & 3;
     const int half = (warp_idx - 2) >> 2;
+    if (p.g_world > 1) gather_remote_shards(p, (int)threadIdx.x - 64, gather_fail);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -733,6 +882,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (p.g_world > 1 && p.g_done && (int)threadIdx.x - 64 < p.g_world) {
+      // our shard may be rewritten after this kernel: wait until no peer reads it any more
+      const int q = (int)threadIdx.x - 64;
+      const uint32_t* my_pad = reinterpret_cast<const uint32_t*>(p.g_signal_ptrs[p.g_rank]);
+      g_wait_flag<true>(my_pad + GS_DONE + q, p.g_epoch, p, 2, q);
     }
   }
 
@@ -884,6 +1039,14 @@ KernelParams make_params(const GemmArgs& a) {
   if (a.aux_out) w = w && a32(a.aux_out);
   if (a.aux_in) w = w && a32(a.aux_in) && a.ld_aux % 16 == 0;
   p.vec32_ok = w ? 1 : 0;
+  p.g_b_ptrs = nullptr; p.g_signal_ptrs = nullptr; p.g_flags = nullptr; p.g_status = nullptr;
+  p.g_ldb = 0; p.g_rank = 0; p.g_world = 1; p.g_rows_per_shard = 0; p.g_done = 0; p.g_epoch = 0;
+  if (a.gather && a.gather->world > 1) {
+    const GemmGather& g = *a.gather;
+    p.g_b_ptrs = g.b_ptrs; p.g_signal_ptrs = g.signal_ptrs; p.g_flags = g.flags;
+    p.g_status = g.status; p.g_ldb = a.ldb; p.g_rank = g.rank; p.g_world = g.world;
+    p.g_rows_per_shard = a.K / g.world; p.g_done = g.done_barrier; p.g_epoch = g.epoch;
+  }
   return p;
 }
 
@@ -1050,7 +1213,7 @@ struct TileChoice { int pair = 0, bn = 128; double cost = 1e30; };
 //   its epilogue     (128 x BN outputs per CTA, about 3 TB/s of stores over the chip),
 // tiles run in waves over the resident CTAs / CTA pairs, and a launch costs a fixed few
 // microseconds (more for cluster launches).
-TileChoice choose_tile(const GemmArgs& a, int K, long long batch, bool c_fp32) {
+TileChoice choose_tile(const GemmArgs& a, int K, long long batch, bool c_fp32, bool pair_only = false) {
   struct Cand { int pair, bn; };
   const Cand cands[7] = {{1, 256}, {1, 192}, {1, 128}, {0, 256}, {0, 192}, {0, 128}, {0, 64}};
   const int sms = num_sms();
@@ -1062,6 +1225,7 @@ TileChoice choose_tile(const GemmArgs& a, int K, long long batch, bool c_fp32) {
     const Cand& c = cands[i];
     const int bn = c.bn;
     if (force && bn != force) continue;
+    if (pair_only && !c.pair) continue;
     if (c.pair) {
       if (clusters <= 0) continue;
       if (a.b_mn_major && (bn / 2) % 64 != 0) continue;   // MN-major B arrives in 64-column chunks
@@ -1181,6 +1345,18 @@ size_t gemm_split_k_workspace_bytes(const GemmArgs& a) {
 cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0) return cudaSuccess;
   if (a.K <= 0) return cudaErrorInvalidValue;
+  if (a.gather && a.gather->world > 1) {
+    // B is gathered inside the kernel: CTA-pair path only
+    const GemmGather& g = *a.gather;
+    const bool ok = gemm_uses_tensor_cores(a) && a.b_mn_major == 1 && a.K % g.world == 0 &&
+                    a.N % 8 == 0 && a.batch_inner <= 1 && a.batch_outer <= 1 &&
+                    a.causal_tiles == 0 && a.M > BM && g.world <= 16 && g.b_ptrs &&
+                    g.signal_ptrs && g.flags;
+    if (!ok) return cudaErrorNotSupported;
+    TileChoice t = choose_tile(a, a.K, 1, a.c_fp32 != 0, true);
+    if (t.cost >= 1e29 || !t.pair) return cudaErrorNotSupported;
+    return launch_choice(t, a, stream);
+  }
   if (!gemm_uses_tensor_cores(a)) return launch_simt(a, stream);
   TileChoice tile;
   int splits = choose_split(a, &tile);

@@ -218,3 +218,49 @@ def broadcast_(t: torch.Tensor, root: int = 0, buf: Optional[SymmetricBuffer] = 
         return t
     dist.broadcast(t, src=root)
     return t
+
+
+# ------------------------------------------------------------------------------ all-gather + GEMM
+class ShardedWeight:
+    """A [K, N] bf16 weight whose row shards are owned by the ranks (rank p owns rows
+    [p K/world, (p+1) K/world)): every rank holds a full-size copy in peer-mapped memory, of
+    which only its own shard has to be current.  `gather_matmul` brings the other shards in
+    from inside the GEMM kernel that consumes the weight.  (No counterpart in the reference,
+    which has no sharding: lua/luatorch/distributed/ddp.lua.)"""
+
+    def __init__(self, K: int, N: int):
+        assert K % max(1, world_size()) == 0 and N % 8 == 0
+        self.K, self.N = K, N
+        self.buf = SymmetricBuffer(K * N * 2)
+        self.weight = self.buf.typed(torch.bfloat16)[: K * N].view(K, N)
+        self.flags = torch.zeros(world_size() + 1, dtype=torch.int32, device=self.weight.device)
+
+    @property
+    def shard(self) -> torch.Tensor:
+        r, w = rank(), world_size()
+        rows = self.K // w
+        return self.weight[r * rows:(r + 1) * rows]
+
+
+def gather_matmul(x: torch.Tensor, w: ShardedWeight, bias: Optional[torch.Tensor] = None,
+                  gelu: bool = False, done_barrier: bool = True) -> torch.Tensor:
+    """y = x @ W (+ bias, GELU) with the all-gather of W's row shards fused into the tcgen05
+    GEMM: the kernel pulls the remote shards over NVLink into the local copy while its first
+    tiles already multiply the local shard, so the transfer overlaps the math and each remote
+    byte crosses the link once.  On return (stream order) `w.weight` is complete on this rank."""
+    M, K = x.shape
+    assert K == w.K and x.dtype == torch.bfloat16 and x.is_contiguous()
+    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+    ws = world_size()
+    if ws > 1 and w.buf.peer_mapped and M > 128:
+        B.ext().gemm_gather(x, w.weight, y, M, w.N, K, K, w.N, w.N, bias, 1 if gelu else 0, None,
+                            w.buf.ptrs, w.buf.signal_ptrs, w.flags, rank(), ws, next_epoch(),
+                            status_buffer(), done_barrier)
+        return y
+    if ws > 1:   # unfused fallback: collective all-gather of the shards, then the plain GEMM
+        parts = [torch.empty_like(w.shard) for _ in range(ws)]
+        dist.all_gather(parts, w.shard.contiguous())
+        w.weight.copy_(torch.cat(parts, 0))
+    B.ext().gemm(x, w.weight, y, M, w.N, K, K, w.N, w.N, False, True, 1, 1, 0, 0, 0, 0, 0, 0, 1.0,
+                 False, bias, 1 if gelu else 0, None, 0, None, None, 0, 0)
+    return y

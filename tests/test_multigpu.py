@@ -124,6 +124,41 @@ def test_fused_allreduce_adamw_modes_match_reference_math():
     """)
 
 
+def test_gather_matmul_fused_allgather_gemm():
+    """Row shards of the weight live on the ranks; the GEMM gathers them itself."""
+    _run("""
+    import torch, torch.distributed as dist
+    import luatorch_b200 as lf
+    from luatorch_b200.distributed import comm
+    comm.init()
+    r, w = comm.rank(), comm.world_size()
+    for (M, K, N, gelu) in [(1024, 768, 3072, True), (8192, 768, 768, False), (512, 2048, 1024, False)]:
+        torch.manual_seed(5)                       # same full weight on every rank
+        full = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
+        bias = torch.randn(N, device="cuda").bfloat16()
+        torch.manual_seed(100 + r)                 # own activations
+        x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        sw = comm.ShardedWeight(K, N)
+        for it in range(3):                        # repeated calls reuse pads and flags
+            sw.weight.zero_()
+            sw.shard.copy_(full[r * (K // w):(r + 1) * (K // w)])
+            torch.cuda.synchronize(); dist.barrier()
+            y = comm.gather_matmul(x, sw, bias, gelu)
+            torch.cuda.synchronize()
+            comm.check_status()
+            assert torch.equal(sw.weight, full), "local copy incomplete after the gather"
+            ref = x.float() @ full.float() + bias.float()
+            if gelu:
+                ref = 0.5 * ref * (1 + torch.tanh(0.7978845608 * (ref + 0.044715 * ref ** 3)))
+            torch.testing.assert_close(y.float(), ref, atol=0.08, rtol=0.03)
+            dist.barrier()
+    from luatorch_b200 import _C
+    assert _C.gemm_device_error() == 0
+    if r == 0: print("CASE_OK")
+    comm.destroy()
+    """)
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     # single GPU is enough: a flag nobody sets makes the wait run out; the context stays usable
     import torch
