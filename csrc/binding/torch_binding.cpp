@@ -150,7 +150,7 @@ void gemm_gather(const Tensor& A, const Tensor& B_local, Tensor& C, int64_t M, i
   gg.status = status.data_ptr<int>();
   gg.done_barrier = done_barrier ? 1 : 0;
   g.gather = &gg;
-  check(cudaMemsetAsync(flags.data_ptr(), 0, (size_t)(world + 1) * 4, cur_stream()), "gemm_gather flags");
+  check(cudaMemsetAsync(flags.data_ptr(), 0, (size_t)flags.numel() * 4, cur_stream()), "gemm_gather flags");
   check(lt::gemm_bf16(g, cur_stream()), "gemm_gather");
 }
 

@@ -405,8 +405,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         lse_l2 = p.lse[idx] * LOG2E;
         delta = p.delta[idx];
       }
-      if (!mbar_wait_bounded(smem_u32(s_full), it & 1, abort_flag, &g_attn_error, 36) ||
-          !mbar_wait_bounded(smem_u32(pds_empty), (it & 1) ^ 1, abort_flag, &g_attn_error, 37)) {
+      if (!mbar_wait_bounded_warp(smem_u32(s_full), it & 1, abort_flag, &g_attn_error, 36) ||
+          !mbar_wait_bounded_warp(smem_u32(pds_empty), (it & 1) ^ 1, abort_flag, &g_attn_error, 37)) {
         ok = false;
         break;
       }
@@ -419,7 +419,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_arrive(smem_u32(pds_full));
     }
     if (ok && n_it > 0 &&
-        mbar_wait_bounded(smem_u32(acc_full), 0, abort_flag, &g_attn_error, 38)) {
+        mbar_wait_bounded_warp(smem_u32(acc_full), 0, abort_flag, &g_attn_error, 38)) {
       tc_fence_after_sync();
       const int gi = own * BT + row;  // key index (DKDV) or query index
       const bool in_range = gi < p.S;

@@ -332,7 +332,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     for (int j = 0; ok && j < n_kv; ++j) {
       const int st = NSB == 2 ? (j & 1) : 0;
       const int su = NSB == 2 ? (j >> 1) : j;
-      if (!mbar_wait_bounded(smem_u32(&s_full[st]), su & 1, abort_flag, &g_attn_error, 18)) {
+      if (!mbar_wait_bounded_warp(smem_u32(&s_full[st]), su & 1, abort_flag, &g_attn_error, 18)) {
         ok = false;
         break;
       }
@@ -368,7 +368,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float alpha = (m == -INFINITY) ? 0.0f : ex2((m - m_new) * c);
       // fold in the previous tile's P V product, then rescale to the new maximum
       if (j > 0) {
-        if (!mbar_wait_bounded(smem_u32(o_full), (j - 1) & 1, abort_flag, &g_attn_error, 19)) {
+        if (!mbar_wait_bounded_warp(smem_u32(o_full), (j - 1) & 1, abort_flag, &g_attn_error, 19)) {
           ok = false;
           break;
         }
@@ -409,7 +409,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_arrive(smem_u32(p_full));
     }
     if (ok && n_kv > 0) {
-      if (mbar_wait_bounded(smem_u32(o_full), (n_kv - 1) & 1, abort_flag, &g_attn_error, 20)) {
+      if (mbar_wait_bounded_warp(smem_u32(o_full), (n_kv - 1) & 1, abort_flag, &g_attn_error, 20)) {
         tc_fence_after_sync();
 #pragma unroll
         for (int c32 = 0; c32 < D / 32; ++c32) {

@@ -430,6 +430,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      // Tail: the last commits onto the "empty" barriers land asynchronously; wait for them
+      // so nothing is still on its way when the CTA exits.
+      for (int s = 0; ok && s < STAGES; ++s) {
+        if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, &g_gemm_error, 5))
+          ok = false;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
       if (!ok) {
         // Give loads already in flight time to land before the CTA releases its
         // shared memory.
@@ -505,7 +512,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = (t / p.tiles_m) * BN;
       if (tile_skipped(m0, n0)) continue;
       const int bi = b % p.batch_inner, bo = b / p.batch_inner;
-      if (!mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, &g_gemm_error,
+      if (!mbar_wait_bounded_warp(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, &g_gemm_error,
                              4)) {
         ok = false;
         break;
@@ -530,6 +537,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // ------------------------------------------------------------------------------
 // All-gather of B fused into the pair kernel (see GemmGather in gemm.h).
 // ------------------------------------------------------------------------------
+#ifndef LT_PAIR_KSUB
+#define LT_PAIR_KSUB 2
+#endif
 constexpr int GS_START = 0, GS_DONE = 16;        // signal-pad slots, as in csrc/comm/comm_kernels.cu
 constexpr long long GATHER_BUDGET = 6000000000ll;  // about three seconds of SM clocks
 
@@ -625,6 +635,7 @@ __device__ void gather_remote_shards(const KernelParams& p, int t, int* sh_fail)
           if (off[u] >= 0) *reinterpret_cast<uint4*>(local + off[u]) = d[u];
       }
     }
+    asm volatile("fence.proxy.async;" ::: "memory");   // these rows are read through TMA next
     __threadfence();
     epi_bar();
     // counted even after a failure, so that no producer waits for a shard in vain (the error
@@ -653,9 +664,6 @@ __device__ void gather_remote_shards(const KernelParams& p, int t, int* sh_fail)
 //          producer refills its own stage when the MMAs that read it have retired;
 //   tmem_full (both CTAs) / tmem_empty (even CTA, one arrive per epilogue warp of both CTAs).
 // ------------------------------------------------------------------------------
-#ifndef LT_PAIR_KSUB
-#define LT_PAIR_KSUB 2
-#endif
 template <int BN>
 struct PairCfg {
   static constexpr int KSUB = LT_PAIR_KSUB;             // 64-wide k blocks per pipeline stage
@@ -798,6 +806,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      // Tail: the MMA thread's commits reach this CTA's "empty" barriers asynchronously (for
+      // the odd CTA from the other SM); nothing may still be on its way when the CTA exits
+      // and its shared memory is handed to another block.
+      for (int s = 0; ok && s < STAGES; ++s) {
+        if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, &g_gemm_error, 15))
+          ok = false;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
@@ -870,7 +886,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int m0 = (t % p.tiles_m) * (2 * BM) + (int)cta_rank * BM;
       const int n0 = (t / p.tiles_m) * BN;
       const int bi = b % p.batch_inner, bo = b / p.batch_inner;
-      if (!mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, &g_gemm_error,
+      if (!mbar_wait_bounded_warp(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, &g_gemm_error,
                              14)) {
         ok = false;
         break;

@@ -73,6 +73,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// Same wait, for code that a WHOLE warp runs and that continues with warp-collective
+// (.sync.aligned) instructions such as tcgen05.ld: lanes may leave the polling loop at
+// different times, so the result is agreed on by a vote, which also brings the warp back
+// together.  Returns true only if every lane saw the phase complete.
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t parity,
+                                                       volatile int* abort_flag, int* err,
+                                                       int code) {
+  const bool ok = mbar_wait_bounded(bar, parity, abort_flag, err, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ----------------------------------------------------------------------------
 // TMA: tiled bulk tensor loads, each CTA fetches its own tiles
 // ----------------------------------------------------------------------------

@@ -10,6 +10,11 @@ For each bucket size it times (CUDA events, max over ranks, after warm-up)
 and reports the achieved fraction of the roofline: the slower of (bytes that must cross
 NVLink per GPU / 770 GB/s per direction, the measured peer-copy rate of this machine class) and
 (local HBM traffic of the AdamW update / measured copy bandwidth).
+
+It then times the all-gather fused into the GEMM (`gather_matmul`: weight row shards pulled
+over NVLink by the kernel that multiplies them) against the unfused pair (process-group
+all_gather, then the same GEMM); roofline = the slower of FLOPs / measured bf16 GEMM peak and
+remote shard bytes / 770 GB/s.
 """
 from __future__ import annotations
 
@@ -94,6 +99,38 @@ def main():
         comm.check_status()
         if rank == 0:
             print("bucket %4d MB (bf16 grads): " % mb + "  ".join("%s %.3f ms (%.0f%% of roofline)" % (a, b, 100 * c) for a, b, c in rows), flush=True)
+    # ---- all-gather fused into the consuming GEMM
+    peak = 1.59e15
+    if os.path.exists(p):
+        peak = json.load(open(p))["bf16_tflops"] * 1e12
+    for (M, K, N) in [(8192, 768, 3072), (8192, 2048, 8192), (8192, 3072, 768), (8192, 768, 50264)]:
+        if K % world:
+            continue
+        sw = comm.ShardedWeight(K, N)
+        sw.weight.copy_((torch.randn(K, N, device="cuda") * 0.02).bfloat16())
+        x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        parts = torch.empty(K, N, device="cuda", dtype=torch.bfloat16)
+
+        def fused_gemm():
+            comm.gather_matmul(x, sw)
+
+        def unfused():
+            dist.all_gather_into_tensor(parts, sw.shard.contiguous())
+            C.gemm(x, parts, y, M, N, K, K, N, N, False, True, 1, 1, 0, 0, 0, 0, 0, 0, 1.0, False, None, 0, None, 0,
+                   None, None, 0, 0)
+
+        def local_only():
+            C.gemm(x, parts, y, M, N, K, K, N, N, False, True, 1, 1, 0, 0, 0, 0, 0, 0, 1.0, False, None, 0, None, 0,
+                   None, None, 0, 0)
+
+        t_f, t_u, t_l = timed(fused_gemm), timed(unfused), timed(local_only)
+        comm.check_status()
+        bound = max(2.0 * M * N * K / peak, K * N * 2.0 * (world - 1) / world / NVLINK_BPS)
+        if rank == 0:
+            print("gather+GEMM [%d,%d]x[%d,%d]: fused %.3f ms (%.0f%% of roofline)  all_gather + GEMM %.3f ms  "
+                  "GEMM alone %.3f ms" % (M, K, K, N, t_f, 100 * bound * 1e3 / t_f, t_u, t_l), flush=True)
+        del sw
     dist.barrier()
     comm.destroy()
 
