@@ -13,6 +13,7 @@
 //        dQ += dS K accumulates in TMEM.
 #include "attention.h"
 #include "sm100_ptx.cuh"
+#include "common.cuh"
 
 #include <cuda.h>
 #include <atomic>
@@ -68,6 +69,7 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
                   float* __restrict__ delta, int B, int H, int S, int D, long long o_sb,
                   long long o_ss, long long o_sh, long long do_sb, long long do_ss,
                   long long do_sh) {
+  pdl_enter();
   const long long r = blockIdx.x * 256ll + threadIdx.x;  // over B*S*H, head fastest
   if (r >= (long long)B * H * S) return;
   const int h = r % H, s = (r / H) % S, b = r / ((long long)S * H);
@@ -241,10 +243,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tmem_alloc(smem_u32(tmem_holder), 512);
     tmem_relinquish();
   }
+  pdl_trigger();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();   // operands come from earlier kernels of the stream
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128;
   const uint32_t tmem_acc0 = tmem_base + 256;        // dK or dQ
   const uint32_t tmem_acc1 = tmem_base + 256 + D;    // dV
@@ -468,7 +472,8 @@ cudaError_t launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  flash_bwd_kernel<D, DKDV><<<grid, NUM_THREADS, L::TOTAL, s>>>(tq, tk, tv, tdo, p);
+  cudaError_t le = launch_pdl(flash_bwd_kernel<D, DKDV>, grid, dim3(NUM_THREADS), L::TOTAL, s, tq, tk, tv, tdo, p);
+  if (le != cudaSuccess) return le;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
@@ -486,9 +491,11 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
     return cudaErrorInvalidValue;
 
   const long long rows = (long long)a.B * a.H * a.S;
-  attn_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, stream>>>(
-      (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)g.d_o, g.delta, a.B, a.H, a.S, a.D, a.o_sb,
-      a.o_ss, a.o_sh, g.do_sb, g.do_ss, g.do_sh);
+  cudaError_t de = launch_pdl(attn_delta_kernel, dim3((unsigned)((rows + 255) / 256)), dim3(256), 0, stream,
+                              (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)g.d_o, g.delta, a.B, a.H,
+                              a.S, a.D, (long long)a.o_sb, (long long)a.o_ss, (long long)a.o_sh,
+                              (long long)g.do_sb, (long long)g.do_ss, (long long)g.do_sh);
+  if (de != cudaSuccess) return de;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
 
   CUtensorMap tq, tk, tv, tdo;

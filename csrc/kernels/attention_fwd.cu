@@ -10,6 +10,7 @@
 // warps are busy with exponentials.  Tiles above the causal diagonal are never loaded.
 #include "attention.h"
 #include "sm100_ptx.cuh"
+#include "common.cuh"
 
 #include <cuda.h>
 #include <atomic>
@@ -219,10 +220,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tmem_alloc(smem_u32(tmem_holder), L::TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_trigger();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();   // q, k, v come from the previous kernel
   const uint32_t tmem_s = tmem_base;                // NSB score buffers of 128 columns
   const uint32_t tmem_o = tmem_base + NSB * 128;    // D columns
 
@@ -471,7 +474,8 @@ cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
   p.lse = a.lse;
   dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
-  flash_fwd_kernel<D><<<grid, NUM_THREADS, L::TOTAL, stream>>>(tq, tk, tv, p);
+  cudaError_t le = launch_pdl(flash_fwd_kernel<D>, grid, dim3(NUM_THREADS), L::TOTAL, stream, tq, tk, tv, p);
+  if (le != cudaSuccess) return le;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }

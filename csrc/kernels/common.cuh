@@ -5,12 +5,56 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <atomic>
 
 namespace lt {
 
 extern std::atomic<uint64_t> g_ops_launches;
 #define LT_COUNT_LAUNCH() ::lt::g_ops_launches.fetch_add(1, std::memory_order_relaxed)
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may be scheduled while
+// the kernel before it in the stream is still running, so its launch latency and prologue
+// overlap that kernel's tail; pdl_wait() then blocks until the earlier kernel has completed
+// and its writes are visible.  Rules: a kernel launched this way touches no global memory
+// before pdl_wait(), and pdl_trigger() (allow the NEXT kernel to be scheduled) may come first
+// because the next kernel waits for this one in the same way.  LT_PDL=0 in the environment
+// turns the launch attribute off (plain stream order).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+  pdl_trigger();
+  pdl_wait();
+}
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LT_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 template <typename T> struct VecIO;
 

@@ -6,6 +6,7 @@
 // Covers the reference kernels K1-K22, K27-K33, K46 and K48 (csrc/cuda/ops/arithmetic.cu,
 // activation.cu, cast.cu, matmul.cu:199-206), which are scalar one-thread-per-element
 // launches of 256-thread blocks there.
+#include <stdlib.h>
 #include "ops.h"
 #include "common.cuh"
 
@@ -290,6 +291,7 @@ colsum_fused(const T* __restrict__ in, int64_t ld, int64_t rows, int64_t cols,
   constexpr int V = VecIO<T>::N;
   __shared__ float sh[8][32 * V + 1];
   __shared__ int is_last;
+  pdl_enter();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t c0 = ((int64_t)blockIdx.x * 32 + lane) * V;
   const bool ok = c0 < cols;
@@ -365,8 +367,8 @@ cudaError_t column_sum(int dtype, const void* in, int64_t ld, void* out, int out
       dim3 g((unsigned)groups, (unsigned)slabs);
       LT_DISPATCH_DTYPE(dtype, T, {
         LT_DISPATCH_DTYPE(out_dtype, TO, {
-          colsum_fused<T, TO><<<g, 256, 0, s>>>((const T*)in, ld, rows, cols, rps, scratch,
-                                                (TO*)out, accumulate);
+          launch_pdl(colsum_fused<T, TO>, g, dim3(256), 0, s, (const T*)in, ld, rows, cols, rps, scratch,
+                     (TO*)out, accumulate);
           LT_COUNT_LAUNCH();
           return cudaGetLastError();
         })

@@ -15,6 +15,7 @@
 // become epilogue options here.
 #include "gemm.h"
 #include "sm100_ptx.cuh"
+#include "common.cuh"
 
 #include <cuda.h>
 #include <atomic>
@@ -371,10 +372,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tmem_alloc(smem_u32(tmem_base_holder), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_trigger();   // the next kernel may be scheduled; it waits for this one in its own prologue
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_holder;
+  pdl_wait();      // everything above overlapped the previous kernel's tail; its results are final now
 
   const int num_kb = (p.K + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -723,10 +726,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_before_sync();
   __syncthreads();
+  pdl_trigger();
   cluster_arrive();          // the peer's barriers exist before anything is sent to them
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_holder;
+  pdl_wait();                // the previous kernel's results are final from here on
 
   const int num_kb = (p.K + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
   const int tiles_per_batch = p.tiles_m * p.tiles_n;     // tiles_m counts 256-row pair tiles
@@ -1098,7 +1103,8 @@ cudaError_t launch_tc(const GemmArgs& a, cudaStream_t stream) {
   if (!ok) return cudaErrorInvalidValue;
   const long long total = (long long)p.tiles_m * p.tiles_n * p.batch_total;
   const int grid = (int)(total < num_sms() ? total : num_sms());
-  gemm_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  cudaError_t le = launch_pdl(gemm_tcgen05_kernel<BN>, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, p);
+  if (le != cudaSuccess) return le;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
@@ -1164,7 +1170,8 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   if (!ok) return cudaErrorInvalidValue;
   const long long total = (long long)p.tiles_m * p.tiles_n * p.batch_total;
   const int grid = 2 * (int)(total < clusters ? total : clusters);
-  gemm_tcgen05_pair_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  cudaError_t le = launch_pdl(gemm_tcgen05_pair_kernel<BN>, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, p);
+  if (le != cudaSuccess) return le;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
@@ -1318,6 +1325,7 @@ cudaError_t launch_choice(const TileChoice& t, const GemmArgs& a, cudaStream_t s
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slice, int M, int N,
                      void* C, long long ldc, int c_fp32, int accumulate) {
+  pdl_enter();
   const long long quads = (long long)M * (N / 4);
   for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < quads;
        q += (long long)gridDim.x * blockDim.x) {
@@ -1406,9 +1414,10 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   const long long quads = (long long)a.M * (a.N / 4);
   int blocks = (int)((quads + 255) / 256);
   if (blocks > 8 * num_sms()) blocks = 8 * num_sms();
-  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>((const float*)a.workspace, splits,
-                                                   (long long)a.M * a.N, a.M, a.N, a.C, a.ldc,
-                                                   a.c_fp32, a.accumulate);
+  cudaError_t re = launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream,
+                              (const float*)a.workspace, splits, (long long)a.M * a.N, a.M, a.N,
+                              a.C, (long long)a.ldc, a.c_fp32, a.accumulate);
+  if (re != cudaSuccess) return re;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }

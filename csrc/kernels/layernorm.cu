@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(THREADS)
 ln_fwd_kernel(const T* __restrict__ x, const TP* __restrict__ gamma, const TP* __restrict__ beta,
               float eps, T* __restrict__ y, float* __restrict__ mean_out,
               float* __restrict__ rstd_out, int64_t rows, int64_t cols) {
+  pdl_enter();
   constexpr int V = VecIO<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t row = blockIdx.x * (int64_t)WARPS + (threadIdx.x >> 5);
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(THREADS)
 ln_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
              const float* __restrict__ mean, const float* __restrict__ rstd,
              const T* __restrict__ dx_add, T* __restrict__ dx, int64_t rows, int64_t cols) {
+  pdl_enter();
   constexpr int V = VecIO<T>::N;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t nvec = cols / V;
@@ -168,6 +170,7 @@ __global__ void __launch_bounds__(THREADS)
 ln_stats_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ mean,
                 const float* __restrict__ rstd, float* __restrict__ scratch, int64_t rows,
                 int64_t cols, int64_t rows_per_slab) {
+  pdl_enter();
   constexpr int V = VecIO<T>::N;
   __shared__ float sh[WARPS][2][32 * V + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -262,6 +265,7 @@ template <typename TG>
 __global__ void __launch_bounds__(256)
 ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
                 TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate) {
+  pdl_enter();
   __shared__ float sh[8][33];
   const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
   const int64_t c = blockIdx.x * 32ll + cx;
@@ -293,9 +297,8 @@ cudaError_t ln_fwd_dispatch(const void* x, const void* gamma, const void* beta, 
   const bool fast = cols % V == 0 && cols <= 32 * 8 * V && is_aligned16(x) && is_aligned16(y);
   const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
 #define LT_LN_FWD(NVV)                                                                       \
-  ln_fwd_kernel<T, TP, NVV><<<grid, THREADS, 0, s>>>((const T*)x, (const TP*)gamma,          \
-                                                     (const TP*)beta, eps, (T*)y, mean, rstd, \
-                                                     rows, cols)
+  launch_pdl(ln_fwd_kernel<T, TP, NVV>, dim3(grid), dim3(THREADS), 0, s, (const T*)x,          \
+             (const TP*)gamma, (const TP*)beta, eps, (T*)y, mean, rstd, rows, cols)
   if (fast) {
     const int64_t per_lane = (cols / V + 31) / 32;
     if (per_lane <= 1) LT_LN_FWD(1);
@@ -322,9 +325,8 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
   if (fast) {
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
 #define LT_LN_BWD(NVV)                                                                       \
-  ln_dx_kernel<T, TP, NVV><<<grid, THREADS, 0, s>>>((const T*)x, (const T*)dy,               \
-                                                    (const TP*)gamma, mean, rstd,            \
-                                                    (const T*)dx_add, (T*)dx, rows, cols)
+  launch_pdl(ln_dx_kernel<T, TP, NVV>, dim3(grid), dim3(THREADS), 0, s, (const T*)x,           \
+             (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx, rows, cols)
     const int64_t per_lane = (cols / V + 31) / 32;
     if (per_lane <= 1) LT_LN_BWD(1);
     else if (per_lane <= 2) LT_LN_BWD(2);
@@ -342,8 +344,8 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
     const int64_t rps = (rows + slabs - 1) / slabs;
     slabs = (int)((rows + rps - 1) / rps);
     *nparts = slabs;
-    ln_stats_kernel<T><<<dim3((unsigned)colgroups, (unsigned)slabs), THREADS, 0, s>>>(
-        (const T*)x, (const T*)dy, mean, rstd, scratch, rows, cols, rps);
+    launch_pdl(ln_stats_kernel<T>, dim3((unsigned)colgroups, (unsigned)slabs), dim3(THREADS), 0, s,
+               (const T*)x, (const T*)dy, mean, rstd, scratch, rows, cols, rps);
     LT_COUNT_LAUNCH();
   } else {
     ln_bwd_generic<T, TP><<<(unsigned)rows, THREADS, 0, s>>>(
@@ -439,8 +441,8 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
   if (e != cudaSuccess) return e;
   if (dgamma && dbeta) {
     LT_DISPATCH_DTYPE(grad_dtype, TG, {
-      ln_param_reduce<TG><<<(unsigned)((2 * cols + 31) / 32), 256, 0, s>>>(
-          scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
+      launch_pdl(ln_param_reduce<TG>, dim3((unsigned)((2 * cols + 31) / 32)), dim3(256), 0, s,
+                 scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
       LT_COUNT_LAUNCH();
     })
   }

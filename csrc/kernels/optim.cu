@@ -60,6 +60,7 @@ adamw_vec_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow,
                  const TG* __restrict__ grad, float* __restrict__ m, float* __restrict__ v,
                  int64_t n4, const int64_t* __restrict__ seg_end, const float* __restrict__ seg_wd,
                  int nseg, AdamArgs a) {
+  pdl_enter();
   if (a.skip_flag && *a.skip_flag) return;
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -136,13 +137,12 @@ cudaError_t adamw_flat(float* master, void* shadow, const void* grad, int grad_d
   if (vec) {
     const int grid = stream_grid(n / 4, THREADS);
     if (grad_dtype == DT_F32)
-      adamw_vec_kernel<float><<<grid, THREADS, 0, s>>>(master, (__nv_bfloat16*)shadow,
-                                                       (const float*)grad, m, v, n / 4, seg_end,
-                                                       seg_wd, nseg, args);
+      launch_pdl(adamw_vec_kernel<float>, dim3(grid), dim3(THREADS), 0, s, master,
+                 (__nv_bfloat16*)shadow, (const float*)grad, m, v, n / 4, seg_end, seg_wd, nseg, args);
     else
-      adamw_vec_kernel<__nv_bfloat16><<<grid, THREADS, 0, s>>>(
-          master, (__nv_bfloat16*)shadow, (const __nv_bfloat16*)grad, m, v, n / 4, seg_end, seg_wd,
-          nseg, args);
+      launch_pdl(adamw_vec_kernel<__nv_bfloat16>, dim3(grid), dim3(THREADS), 0, s, master,
+                 (__nv_bfloat16*)shadow, (const __nv_bfloat16*)grad, m, v, n / 4, seg_end, seg_wd,
+                 nseg, args);
   } else {
     const int grid = stream_grid(n, THREADS);
     if (grad_dtype == DT_F32)

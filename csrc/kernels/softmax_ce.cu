@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(THREADS)
 ce_forward_kernel(const T* __restrict__ logits, int64_t ld, const void* __restrict__ labels,
                   int label_kind, int64_t cols, float* __restrict__ lse,
                   float* __restrict__ row_loss, int* err_flag, int vec_base_ok) {
+  pdl_enter();
   __shared__ float sh_m[32], sh_s[32];
   const int64_t r = blockIdx.x;
   const T* row = logits + r * ld;
@@ -175,6 +176,7 @@ ce_backward_kernel(const T* logits, int64_t ld, const void* __restrict__ labels,
                    int64_t cols, const float* __restrict__ lse, float grad_scale,
                    const float* __restrict__ gs_dev, T* dlogits, int64_t ld_out,
                    int vec_base_ok) {
+  pdl_enter();
   constexpr int V = VecIO<T>::N;
   const int64_t r = blockIdx.x;
   const T* row = logits + r * ld;
@@ -259,9 +261,8 @@ cudaError_t cross_entropy_forward(int dtype, const void* logits, int64_t ld, con
   if (rows <= 0) return cudaSuccess;
   const int vec = is_aligned16(logits);
   LT_DISPATCH_DTYPE(dtype, T, {
-    ce_forward_kernel<T><<<(unsigned)rows, THREADS, 0, s>>>((const T*)logits, ld, labels,
-                                                            label_kind, cols, lse, row_loss,
-                                                            err_flag, vec);
+    launch_pdl(ce_forward_kernel<T>, dim3((unsigned)rows), dim3(THREADS), 0, s, (const T*)logits, ld,
+               labels, label_kind, cols, lse, row_loss, err_flag, vec);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })
@@ -275,9 +276,8 @@ cudaError_t cross_entropy_backward(int dtype, const void* logits, int64_t ld, co
   if (rows <= 0) return cudaSuccess;
   const int vec = is_aligned16(logits) && is_aligned16(dlogits);
   LT_DISPATCH_DTYPE(dtype, T, {
-    ce_backward_kernel<T><<<(unsigned)rows, THREADS, 0, s>>>((const T*)logits, ld, labels,
-                                                             label_kind, cols, lse, grad_scale,
-                                                             gs_dev, (T*)dlogits, ld_out, vec);
+    launch_pdl(ce_backward_kernel<T>, dim3((unsigned)rows), dim3(THREADS), 0, s, (const T*)logits, ld,
+               labels, label_kind, cols, lse, grad_scale, gs_dev, (T*)dlogits, ld_out, vec);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })
