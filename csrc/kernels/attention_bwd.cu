@@ -97,17 +97,20 @@ __device__ __forceinline__ void rebuild_chunk(const uint32_t (&s)[32], const uin
                                               float scale, uint8_t* p_dst, uint8_t* ds_dst,
                                               int c32, int row) {
   uint32_t pp[16], dd[16];
+  // two scores per instruction on the FMA pipe: x = s c - lse, g = dp scale - delta scale
+  const float2 cc = make_float2(c, c), ll = make_float2(-lse_l2, -lse_l2);
+  const float2 ss = make_float2(scale, scale), dl = make_float2(-delta * scale, -delta * scale);
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    float p0 = ex2(fmaf(__uint_as_float(s[i]), c, -lse_l2));
-    float p1 = ex2(fmaf(__uint_as_float(s[i + 1]), c, -lse_l2));
+    const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), cc, ll);
+    float2 pv = make_float2(ex2(x.x), ex2(x.y));
     if (MASKED) {
-      p0 = (i < valid) ? p0 : 0.0f;
-      p1 = (i + 1 < valid) ? p1 : 0.0f;
+      pv.x = (i < valid) ? pv.x : 0.0f;
+      pv.y = (i + 1 < valid) ? pv.y : 0.0f;
     }
-    const float d0 = p0 * (__uint_as_float(dp[i]) - delta) * scale;
-    const float d1 = p1 * (__uint_as_float(dp[i + 1]) - delta) * scale;
-    __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+    const float2 g = ffma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ss, dl);
+    const float2 dv = fmul2(pv, g);
+    __nv_bfloat162 hp = __floats2bfloat162_rn(pv.x, pv.y), hd = __floats2bfloat162_rn(dv.x, dv.y);
     pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
     dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
   }
