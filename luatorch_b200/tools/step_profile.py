@@ -6,15 +6,22 @@ clock state the step gives them, unlike a kernel-replay profiler).
 Uses the CUPTI activity records that torch.profiler collects: one line per kernel family with
 launches per step, time per step, share of the GPU-busy time and mean duration, plus the span
 of a step and the idle gaps between kernels.  The records cost a little host time per launch,
-so use the table for SHARES; throughput numbers come from bench.py, which runs unprofiled.
+so use the table for SHARES; throughput numbers come from bench.py, which runs unprofiled
+(and with programmatic dependent launch on, which this tool switches off for attribution).
 (The reference has no counterpart: its tools/benchmark.lua times whole ops with os.clock().)
 """
 from __future__ import annotations
 
 import argparse
 import collections
+import os
 import re
 import sys
+
+# With programmatic dependent launch a kernel's recorded duration includes the time it spends
+# waiting for its predecessor, which makes per-kernel shares meaningless; the breakdown is
+# therefore taken in plain stream order unless the caller sets LT_PDL explicitly.
+os.environ.setdefault("LT_PDL", "0")
 
 import torch
 
