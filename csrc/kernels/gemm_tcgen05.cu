@@ -1217,9 +1217,10 @@ bool gemm_uses_tensor_cores(const GemmArgs& a) {
   if (a.a_stride_inner % 8 || a.a_stride_outer % 8 || a.b_stride_inner % 8 ||
       a.b_stride_outer % 8)
     return false;
-  // Tiny problems are not worth a 128-row tile.
-  if ((long long)a.M * a.N < 64 * 64 && a.batch_inner * a.batch_outer == 1) return false;
-  if (a.N < 16) return false;
+  // Tiny problems are not worth a 128-row tile (a small output with a long K is not tiny:
+  // convolution weight gradients have K = batch x pixels).
+  if ((long long)a.M * a.N < 64 * 64 && a.K < 1024 && a.batch_inner * a.batch_outer == 1) return false;
+  if (a.N < 8) return false;
   return true;
 }
 
@@ -1292,8 +1293,8 @@ int choose_split(const GemmArgs& a, TileChoice* slice_tile) {
     return 1;
   int best_s = 1;
   double best_cost = whole.cost;
-  const int splits[7] = {2, 3, 4, 6, 8, 12, 16};
-  for (int i = 0; i < 7; ++i) {
+  const int splits[11] = {2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
+  for (int i = 0; i < 11; ++i) {
     const int s = splits[i];
     if (a.K % (s * BK) != 0 || a.K / s < 8 * BK) continue;
     TileChoice t = choose_tile(a, a.K / s, s, true);

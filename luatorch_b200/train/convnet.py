@@ -17,7 +17,7 @@ class ConvNet(lf.nn.Module):
     def __init__(self):
         nn = lf.nn
         self.c1, self.c2, self.c3 = nn.Conv2d(3, 32, 3, 1, 1), nn.Conv2d(32, 64, 3, 2, 1), nn.Conv2d(64, 128, 3, 2, 1)
-        self.fc = nn.Linear(8192, 10)
+        self.fc = nn.Linear(8192, 10, pad_out=True)   # row stride 16: TMA-addressable, tensor-core path
 
     def children(self):
         return [self.c1, self.c2, self.c3, self.fc]
