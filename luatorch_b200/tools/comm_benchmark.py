@@ -7,8 +7,8 @@ For each bucket size it times (CUDA events, max over ranks, after warm-up)
                     all-gather by peer stores
   fused-replicated  one launch: every rank reduces the whole bucket and updates its replica
   nccl + adamw      ncclAllReduce on the bf16 gradients, then the flat AdamW launch
-and reports the achieved fraction of the roofline: the slower of (bytes that must cross
-NVLink per GPU / 770 GB/s per direction, the measured peer-copy rate of this machine class) and
+and reports the achieved fraction of the roofline: the slower of (bytes that must ENTER a GPU
+over NVLink / 770 GB/s per direction, the measured peer-copy rate of this machine class) and
 (local HBM traffic of the AdamW update / measured copy bandwidth).
 
 It then times the all-gather fused into the GEMM (`gather_matmul`: weight row shards pulled
@@ -89,9 +89,12 @@ def main():
 
         rows = []
         for name, fn, link_bytes, hbm_bytes in [
-            ("fused-sharded", lambda: fused(1), nbytes * (world - 1) / world, n / world * 26.0 + nbytes / world * 2),
+            # bytes ENTERING a GPU over NVLink: a two-shot all-reduce brings in (W-1)/W of the
+            # bucket as read responses of the reduce-scatter and another (W-1)/W as the peers'
+            # all-gather stores; the one-shot form reads the whole bucket from every peer
+            ("fused-sharded", lambda: fused(1), 2.0 * nbytes * (world - 1) / world, n / world * 26.0 + nbytes / world * 2),
             ("fused-replicated", lambda: fused(0), nbytes * (world - 1), n * 26.0 + nbytes),
-            ("nccl + adamw", nccl_path, nbytes * (world - 1) / world, n * 28.0),
+            ("nccl + adamw", nccl_path, 2.0 * nbytes * (world - 1) / world, n * 28.0),
         ]:
             ms = timed(fn)
             bound_s = max(link_bytes / NVLINK_BPS, hbm_bytes / hbm)
