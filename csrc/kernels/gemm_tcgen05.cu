@@ -222,24 +222,16 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
   for (int cb = half * HALF_COLS; cb < (half + 1) * HALF_COLS; cb += EPI_CW) {
     if (n0 + cb >= p.N) break;  // uniform across the warp
     uint32_t rr[EPI_CW];
-#ifndef LT_GEMM_DBG_NO_EPI
 #pragma unroll
     for (int s = 0; s < EPI_CW / 32; ++s)
       tmem_ld_32x32(t_row + cb + 32 * s, *reinterpret_cast<uint32_t(*)[32]>(&rr[32 * s]));
     tmem_ld_wait();
-#endif
 #pragma unroll
     for (int s = 0; s < EPI_CW / 32; ++s) {
     const int c0 = cb + 32 * s;
     const int col0 = n0 + c0;
     if (col0 >= p.N) break;
     const uint32_t* r = &rr[32 * s];
-#ifdef LT_GEMM_DBG_NO_EPI
-    continue;
-#endif
-#ifdef LT_GEMM_DBG_NO_STORE
-    if (r[0] != 0x7fc12345u) continue;
-#endif
     if (!row_ok) continue;
     if (p.vec_ok && col0 + 32 <= p.N) {
       float v[32];
@@ -782,11 +774,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           // bytes of both CTAs land on the even CTA's barrier
           const uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
-#ifdef LT_GEMM_DBG_NO_TMA
-          if (cta_rank == 0) mbar_arrive(smem_u32(&full_bar[stage]));
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          continue;
-#endif
           if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * Cfg::STAGE_BYTES);
 #pragma unroll
           for (int sub = 0; sub < Cfg::KSUB; ++sub) {
@@ -858,9 +845,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES + sub * Cfg::B_SUB_BYTES), b_lbo, 1024);
 #pragma unroll
             for (int j = 0; j < BK / UMMA_K; ++j) {
-#ifdef LT_GEMM_DBG_NO_MMA
-              continue;
-#endif
               umma_bf16_pair(d_tmem, a_desc + (uint64_t)(j * a_step),
                              b_desc + (uint64_t)(j * b_step), idesc,
                              (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
