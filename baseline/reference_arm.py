@@ -289,6 +289,50 @@ class Replica:
         return float(v)
 
 
+class _ClockSampler:
+    """SM clocks and throttle reasons of GPU 0 during the timed region (nvidia-smi, 200 ms)."""
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        import subprocess
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            return None
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            sm.append(int(f[0]))
+            mx = max(mx, int(f[1]) if f[1].isdigit() else 0)
+            for nm, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return None
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
 def run(args, cfg):
     def emit(obj):
         obj["impl"] = "reference"
@@ -348,6 +392,8 @@ def run(args, cfg):
     for _ in range(warmup):
         step()
     sync()
+    sampler = _ClockSampler()
+    sampler.start()
     ev0, ev1 = C.c_void_p(), C.c_void_p()
     rt.cudaSetDevice(0)
     rt.cudaEventCreate(C.byref(ev0))
@@ -362,6 +408,7 @@ def run(args, cfg):
     rt.cudaEventSynchronize(ev1)
     ms = C.c_float(0)
     rt.cudaEventElapsedTime(C.byref(ms), ev0, ev1)
+    clocks = sampler.stop()
     tokens_per_step = cfg["micro_batch"] * cfg["seq"] * n
     value = tokens_per_step * steps_run / (ms.value * 1e-3)
     emit({"metric": "GPT training tokens/sec (device-timed, max over ranks)", "value": value,
@@ -376,6 +423,6 @@ def run(args, cfg):
           "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * n,
                   "note": "the loss is read back every step; the C ABI has no GPU embedding gather, so "
                           "token upload is not part of the reference's GPU path"},
-          "final_loss": loss})
+          "gpu_launches": None, "clocks": clocks, "final_loss": loss})
     if n > 1:
         lib.luatorch_nccl_destroy()
