@@ -336,6 +336,24 @@ std::vector<Tensor> cross_entropy_forward(const Tensor& logits, int64_t cols, co
                        loss.data_ptr<float>(), reduce_scratch(), cur_stream()), "reduce_all");
   return {loss, lse, err};
 }
+// as cross_entropy_forward, and `logits` is overwritten with (softmax - onehot) * grad_scale
+std::vector<Tensor> cross_entropy_fused(Tensor& logits, int64_t cols, const Tensor& labels,
+                                        double grad_scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  need_cuda_contig(labels, "labels");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t rows = logits.size(0);
+  auto fo = logits.options().dtype(at::kFloat);
+  Tensor lse = at::empty({rows}, fo), row_loss = at::empty({rows}, fo), loss = at::empty({1}, fo);
+  Tensor err = at::zeros({1}, logits.options().dtype(at::kInt));
+  check(lt::cross_entropy_fused(dt(logits), logits.data_ptr(), logits.stride(0), labels.data_ptr(),
+                                label_kind(labels), rows, cols, lse.data_ptr<float>(),
+                                row_loss.data_ptr<float>(), err.data_ptr<int>(), (float)grad_scale,
+                                cur_stream()), "cross_entropy_fused");
+  check(lt::reduce_all(lt::RED_SUM, lt::DT_F32, row_loss.data_ptr(), rows, 1.0f / (float)rows,
+                       loss.data_ptr<float>(), reduce_scratch(), cur_stream()), "reduce_all");
+  return {loss, lse, err};
+}
 // dlogits written into `out` (may alias logits)
 void cross_entropy_backward(const Tensor& logits, int64_t cols, const Tensor& labels,
                             const Tensor& lse, double grad_scale, const OptT& gs_dev, Tensor& out) {
@@ -663,6 +681,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("softmax_scores_backward", &softmax_scores_backward);
   m.def("cross_entropy_forward", &cross_entropy_forward);
   m.def("cross_entropy_backward", &cross_entropy_backward);
+  m.def("cross_entropy_fused", &cross_entropy_fused);
   m.def("pointwise_loss", &pointwise_loss);
   m.def("pointwise_loss_backward", &pointwise_loss_backward);
   m.def("layernorm_forward", &layernorm_forward);

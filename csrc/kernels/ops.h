@@ -78,6 +78,10 @@ cudaError_t cross_entropy_forward(int dtype, const void* logits, int64_t ld, con
                                   int label_kind, int64_t rows, int64_t cols, float* lse,
                                   float* row_loss, int* err_flag, cudaStream_t s);
 // dlogits = (softmax - onehot) * grad_scale (grad_scale read from device if gs_dev != null)
+// Forward + backward in one kernel: on return `logits` holds (softmax - onehot) * grad_scale.
+cudaError_t cross_entropy_fused(int dtype, void* logits, int64_t ld, const void* labels,
+                                int label_kind, int64_t rows, int64_t cols, float* lse,
+                                float* row_loss, int* err_flag, float grad_scale, cudaStream_t s);
 cudaError_t cross_entropy_backward(int dtype, const void* logits, int64_t ld, const void* labels,
                                    int label_kind, int64_t rows, int64_t cols, const float* lse,
                                    float grad_scale, const float* gs_dev, void* dlogits,

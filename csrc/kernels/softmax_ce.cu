@@ -208,6 +208,59 @@ ce_backward_kernel(const T* logits, int64_t ld, const void* __restrict__ labels,
   }
 }
 
+// Forward and backward in one pass over the logits (training with the gradient written in
+// place): per row, max / sum (first read from DRAM), then loss, and the row is read again
+// (from L2: 512-thread blocks keep the rows in flight under half of the L2 size) and overwritten
+// with (softmax - onehot) * grad_scale.  Halves the DRAM traffic of separate forward + backward.
+template <typename T>
+__global__ void __launch_bounds__(512)
+ce_fused_kernel(T* logits, int64_t ld, const void* __restrict__ labels, int label_kind,
+                int64_t cols, float* __restrict__ lse, float* __restrict__ row_loss, int* err_flag,
+                float grad_scale, int vec_base_ok) {
+  pdl_enter();
+  constexpr int V = VecIO<T>::N;
+  __shared__ float sh_m[32], sh_s[32];
+  const int64_t r = blockIdx.x;
+  T* row = logits + r * ld;
+  const bool vec_ok = vec_base_ok && (ld % V == 0);
+  MaxSum ms = ms_block(row_maxsum<T>(row, cols, vec_ok), sh_m, sh_s);
+  const float l = ms.m + __logf(ms.s);
+  int64_t lab = read_label(labels, label_kind, r);
+  const bool bad = lab < 0 || lab >= cols;
+  if (threadIdx.x == 0) {
+    lse[r] = l;
+    if (bad) {
+      if (err_flag) atomicOr(err_flag, 1);
+      row_loss[r] = 0.0f;
+    } else {
+      row_loss[r] = l - VecIO<T>::ld(row + lab);
+    }
+  }
+  __syncthreads();   // the label's logit has been read before the row is overwritten
+  if (bad) lab = -1;
+  int64_t done = 0;
+  if (vec_ok) {
+    const int64_t nvec = cols / V;
+    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+      float x[V];
+      VecIO<T>::load(row + i * V, x);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float pj = __expf(x[j] - l);
+        if (i * V + j == lab) pj -= 1.0f;
+        x[j] = pj * grad_scale;
+      }
+      VecIO<T>::store(row + i * V, x);
+    }
+    done = nvec * V;
+  }
+  for (int64_t i = done + threadIdx.x; i < cols; i += blockDim.x) {
+    float pj = __expf(VecIO<T>::ld(row + i) - l);
+    if (i == lab) pj -= 1.0f;
+    VecIO<T>::st(row + i, pj * grad_scale);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 pointwise_loss_bwd_kernel(const T* __restrict__ pred, const T* __restrict__ target, int64_t n,
@@ -263,6 +316,20 @@ cudaError_t cross_entropy_forward(int dtype, const void* logits, int64_t ld, con
   LT_DISPATCH_DTYPE(dtype, T, {
     launch_pdl(ce_forward_kernel<T>, dim3((unsigned)rows), dim3(THREADS), 0, s, (const T*)logits, ld,
                labels, label_kind, cols, lse, row_loss, err_flag, vec);
+    LT_COUNT_LAUNCH();
+    return cudaGetLastError();
+  })
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t cross_entropy_fused(int dtype, void* logits, int64_t ld, const void* labels,
+                                int label_kind, int64_t rows, int64_t cols, float* lse,
+                                float* row_loss, int* err_flag, float grad_scale, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  const int vec = is_aligned16(logits);
+  LT_DISPATCH_DTYPE(dtype, T, {
+    launch_pdl(ce_fused_kernel<T>, dim3((unsigned)rows), dim3(512), 0, s, (T*)logits, ld, labels,
+               label_kind, cols, lse, row_loss, err_flag, grad_scale, vec);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })

@@ -66,7 +66,15 @@ class CrossEntropyLoss(Module):
         if logits.is_cuda:
             if not labels.is_cuda:
                 labels = labels.cuda()
-            loss, lse, err = B.cross_entropy_device(logits, labels, cols)
+            fused = (self.inplace_backward and autograd.enabled and pred.requires_grad
+                     and logits.stride(-1) == 1)
+            if fused:
+                # one kernel: loss, log-sum-exp, and the logits overwritten by their gradient
+                # for an upstream gradient of 1 (rescaled in backward if it is not)
+                loss, lse, err = B.ext().cross_entropy_fused(logits, cols, B._labels(labels),
+                                                              1.0 / logits.shape[0])
+            else:
+                loss, lse, err = B.cross_entropy_device(logits, labels, cols)
             self.last_error_flag = err
         else:
             r = B.cross_entropy_full(logits, labels, cols)
@@ -78,11 +86,21 @@ class CrossEntropyLoss(Module):
         out = Tensor(_data=loss)
         inplace = self.inplace_backward
 
+        fused_done = logits.is_cuda and fused
+
         def grad_fn(g):
             if pred.requires_grad:
                 s, dev = _upstream_scale(g)
-                dl = B.cross_entropy_backward(logits, labels, lse, s, out=logits if inplace else None,
-                                              n_classes=cols, scale_dev=dev)
+                if fused_done:
+                    dl = logits                      # already (softmax - onehot) / rows
+                    if dev is not None:
+                        dl[:, :cols].mul_(dev * s)
+                    elif s != 1.0:
+                        dl[:, :cols].mul_(s)
+                else:
+                    dl = B.cross_entropy_backward(logits, labels, lse, s,
+                                                  out=logits if inplace else None,
+                                                  n_classes=cols, scale_dev=dev)
                 autograd.acc_grad(pred, dl)
 
         autograd.record("cross_entropy_loss", [pred], out, grad_fn)

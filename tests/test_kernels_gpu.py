@@ -229,6 +229,23 @@ def test_softmax_and_cross_entropy(C, rows, cols, dtype):
     assert C.cross_entropy_forward(logits, cols, bad)[2].item() == 1
 
 
+@pytest.mark.parametrize("rows,cols,ld", [(64, 1000, 1000), (33, 50257, 50264)])
+def test_cross_entropy_fused_forward_backward(C, rows, cols, ld):
+    """One kernel: loss + log-sum-exp, logits overwritten by (softmax - onehot) * scale."""
+    torch.manual_seed(4)
+    buf = torch.zeros(rows, ld, device="cuda", dtype=torch.bfloat16)
+    buf[:, :cols] = (torch.randn(rows, cols, device="cuda") * 2).bfloat16()
+    labels = torch.randint(0, cols, (rows,), device="cuda")
+    x = buf[:, :cols].float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(x, labels)
+    ref.backward()
+    loss, lse, err = C.cross_entropy_fused(buf, cols, labels, 1.0 / rows)
+    assert err.item() == 0
+    torch.testing.assert_close(loss[0], ref.detach(), atol=2e-3, rtol=2e-3)
+    torch.testing.assert_close(lse, torch.logsumexp(x.detach(), dim=1), atol=2e-3, rtol=2e-3)
+    torch.testing.assert_close(buf[:, :cols].float(), x.grad, atol=2e-4, rtol=3e-2)
+
+
 def test_pointwise_losses(C):
     torch.manual_seed(7)
     p = torch.randn(1000, device="cuda")
