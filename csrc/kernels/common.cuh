@@ -64,6 +64,12 @@ template <> struct VecIO<float> {
     float4 v = *reinterpret_cast<const float4*>(p);
     f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
   }
+  // 16 bytes kept as loaded (registers: 4), converted to fp32 only where they are used
+  __device__ static __forceinline__ uint4 load_raw(const float* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static __forceinline__ void unpack(const uint4& u, float (&f)[4]) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y);
+    f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
   __device__ static __forceinline__ void store(float* p, const float (&f)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
   }
@@ -75,6 +81,10 @@ template <> struct VecIO<__nv_bfloat16> {
   static constexpr int N = 8;
   __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
     uint4 u = *reinterpret_cast<const uint4*>(p);
+    unpack(u, f);
+  }
+  __device__ static __forceinline__ uint4 load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -95,6 +105,15 @@ template <> struct VecIO<__nv_bfloat16> {
 
 template <> struct VecIO<__half> {
   static constexpr int N = 8;
+  __device__ static __forceinline__ uint4 load_raw(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
   __device__ static __forceinline__ void load(const __half* p, float (&f)[8]) {
     uint4 u = *reinterpret_cast<const uint4*>(p);
     const __half2* h = reinterpret_cast<const __half2*>(&u);

@@ -118,14 +118,14 @@ ln_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __rest
        row += (int64_t)gridDim.x * WARPS) {
     const T* xr = x + row * cols;
     const T* dyr = dy + row * cols;
-    float xv[NV][V], g[NV][V], o[NV][V];
+    // x and dy stay in registers as loaded (16 bytes per vector) between the two passes
+    uint4 xraw[NV], graw[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
-        VecIO<T>::load(xr + vi * V, xv[i]);
-        VecIO<T>::load(dyr + vi * V, g[i]);
-        if (dx_add) VecIO<T>::load(dx_add + row * cols + vi * V, o[i]);
+        xraw[i] = VecIO<T>::load_raw(xr + vi * V);
+        graw[i] = VecIO<T>::load_raw(dyr + vi * V);
       }
     }
     const float mu = mean[row], rs = rstd[row];
@@ -134,12 +134,14 @@ ln_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __rest
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
+        float xv[V], g[V];
+        VecIO<T>::unpack(xraw[i], xv);
+        VecIO<T>::unpack(graw[i], g);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          xv[i][j] = (xv[i][j] - mu) * rs;              // x_hat
-          g[i][j] *= ldp(gamma, vi * V + j);            // dy * gamma
-          c1 += g[i][j];
-          c2 += g[i][j] * xv[i][j];
+          const float gg = g[j] * ldp(gamma, vi * V + j);   // dy * gamma
+          c1 += gg;
+          c2 += gg * ((xv[j] - mu) * rs);
         }
       }
     }
@@ -150,12 +152,18 @@ ln_dx_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __rest
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
+        // the residual-stream gradient is fetched here, not with x and dy: keeping it in
+        // registers across the reductions would cost a third row of registers per lane
+        float o[V], xv[V], g[V];
+        if (dx_add) VecIO<T>::load(dx_add + row * cols + vi * V, o);
+        VecIO<T>::unpack(xraw[i], xv);
+        VecIO<T>::unpack(graw[i], g);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float r = rs * (g[i][j] - c1 - xv[i][j] * c2);
-          o[i][j] = dx_add ? o[i][j] + r : r;
+          const float r = rs * (g[j] * ldp(gamma, vi * V + j) - c1 - (xv[j] - mu) * rs * c2);
+          o[j] = dx_add ? o[j] + r : r;
         }
-        VecIO<T>::store(dxr + vi * V, o[i]);
+        VecIO<T>::store(dxr + vi * V, o);
       }
     }
   }
