@@ -1,6 +1,7 @@
 // PyTorch-facing binding of the sm_100a kernels (module `luatorch_b200._C`).
 // Tensors are only used for their storage: every kernel launch goes through the raw-pointer
 // interfaces in csrc/kernels/ops.h and csrc/kernels/gemm.h on the current CUDA stream.
+#include <cstdlib>
 #include <torch/extension.h>
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -592,6 +593,13 @@ std::vector<Tensor> flash_backward(const Tensor& q, const Tensor& k, const Tenso
   b.dk_sb = dk.stride(0); b.dk_ss = dk.stride(1); b.dk_sh = dk.stride(2);
   b.dv_sb = dv.stride(0); b.dv_ss = dv.stride(1); b.dv_sh = dv.stride(2);
   b.delta = delta.data_ptr<float>();
+  // scratch for the dS tiles (dQ = dS K as a GEMM); LT_FLASH_DQ_GEMM=0 keeps the third kernel
+  Tensor ds;
+  static const bool dq_gemm = [] { const char* e = getenv("LT_FLASH_DQ_GEMM"); return !(e && e[0] == '0'); }();
+  if (dq_gemm && S % 128 == 0) {
+    ds = at::empty({B, H, S, S}, q.options());
+    b.ds_scratch = ds.data_ptr();
+  }
   check(lt::flash_attention_backward(a, b, cur_stream()), "flash_attention_backward");
   return {dq, dk, dv};
 }

@@ -34,6 +34,10 @@ struct AttnBwdArgs {
   int64_t dk_sb = 0, dk_ss = 0, dk_sh = 0;
   int64_t dv_sb = 0, dv_ss = 0, dv_sh = 0;
   float* delta = nullptr;           // scratch [B, H, S]: rowsum(dO * O)
+  // Optional bf16 scratch [B, H, S, S].  When given (and S is a multiple of 128) the dK/dV
+  // kernel also writes its dS tiles there and dQ = dS K runs as a batched tensor-core GEMM
+  // over them instead of a third kernel that would rebuild S, dP and dS a second time.
+  void* ds_scratch = nullptr;
 };
 
 cudaError_t flash_attention_forward(const AttnArgs& a, cudaStream_t stream);

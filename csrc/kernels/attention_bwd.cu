@@ -14,6 +14,7 @@
 #include "attention.h"
 #include "sm100_ptx.cuh"
 #include "common.cuh"
+#include "gemm.h"
 
 #include <cuda.h>
 #include <atomic>
@@ -59,6 +60,7 @@ struct BwdParams {
   long long o0_sb, o0_ss, o0_sh;
   __nv_bfloat16* out1;  // dV (kernel 2)
   long long o1_sb, o1_ss, o1_sh;
+  __nv_bfloat16* ds_out;  // optional [B, H, S, S]: dS tiles for the dQ GEMM (dK/dV kernel only)
 };
 
 // ------------------------------------------------------------------ delta = rowsum(dO * O)
@@ -95,7 +97,7 @@ template <bool WRITE_P, bool MASKED>
 __device__ __forceinline__ void rebuild_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32],
                                               int valid, float lse_l2, float delta, float c,
                                               float scale, uint8_t* p_dst, uint8_t* ds_dst,
-                                              int c32, int row) {
+                                              int c32, int row, __nv_bfloat16* ds_global) {
   uint32_t pp[16], dd[16];
   // two scores per instruction on the FMA pipe: x = s c - lse, g = dp scale - delta scale
   const float2 cc = make_float2(c, c), ll = make_float2(-lse_l2, -lse_l2);
@@ -123,6 +125,12 @@ __device__ __forceinline__ void rebuild_chunk(const uint32_t (&s)[32], const uin
     *reinterpret_cast<uint4*>(ds_dst + chunk16) =
         make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
   }
+  if (ds_global) {   // the same 32 values, row-major, for the dQ GEMM
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+      *reinterpret_cast<uint4*>(ds_global + 8 * t) =
+          make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
+  }
 }
 
 // This warp's half (`col_half`) of one query row: two 32-column chunks of S and dP.  No
@@ -132,7 +140,8 @@ template <bool WRITE_P>
 __device__ __forceinline__ void rebuild_row(uint32_t tmem_s, uint32_t tmem_dp, uint32_t lane_base,
                                             int row, int valid, bool masked, float lse_l2,
                                             float delta, float c, float scale, uint8_t* p_tile,
-                                            uint8_t* ds_tile, int col_half) {
+                                            uint8_t* ds_tile, int col_half,
+                                            __nv_bfloat16* ds_row_global) {
   const int row_off = (row >> 3) * 1024 + (row & 7) * 128 + col_half * CHUNK_BYTES;
   const int col0 = col_half * 64;
   uint32_t s0[32], d0[32], s1[32], d1[32];
@@ -143,16 +152,16 @@ __device__ __forceinline__ void rebuild_row(uint32_t tmem_s, uint32_t tmem_dp, u
   tmem_ld_32x32(tmem_dp + lane_base + col0 + 32, d1);
   if (masked) {
     rebuild_chunk<WRITE_P, true>(s0, d0, valid - col0, lse_l2, delta, c, scale, p_tile + row_off,
-                                 ds_tile + row_off, 0, row);
+                                 ds_tile + row_off, 0, row, ds_row_global ? ds_row_global + col0 : nullptr);
     tmem_ld_wait();
     rebuild_chunk<WRITE_P, true>(s1, d1, valid - col0 - 32, lse_l2, delta, c, scale,
-                                 p_tile + row_off, ds_tile + row_off, 1, row);
+                                 p_tile + row_off, ds_tile + row_off, 1, row, ds_row_global ? ds_row_global + col0 + 32 : nullptr);
   } else {
     rebuild_chunk<WRITE_P, false>(s0, d0, 32, lse_l2, delta, c, scale, p_tile + row_off,
-                                  ds_tile + row_off, 0, row);
+                                  ds_tile + row_off, 0, row, ds_row_global ? ds_row_global + col0 : nullptr);
     tmem_ld_wait();
     rebuild_chunk<WRITE_P, false>(s1, d1, 32, lse_l2, delta, c, scale, p_tile + row_off,
-                                  ds_tile + row_off, 1, row);
+                                  ds_tile + row_off, 1, row, ds_row_global ? ds_row_global + col0 + 32 : nullptr);
   }
 }
 
@@ -418,8 +427,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         break;
       }
       tc_fence_after_sync();
+      __nv_bfloat16* ds_row = nullptr;
+      if (DKDV && p.ds_out && qi < p.S)
+        ds_row = p.ds_out + (((long long)b * p.H + h) * p.S + qi) * p.S + k0;
       rebuild_row<DKDV>(tmem_s, tmem_dp, lane_base, row, valid, tile_masked, lse_l2, delta,
-                        p.scale_log2, p.scale, smem + L::OFF_P, smem + L::OFF_DS, col_half);
+                        p.scale_log2, p.scale, smem + L::OFF_P, smem + L::OFF_DS, col_half, ds_row);
       tc_fence_before_sync();
       mbar_arrive(smem_u32(s_empty));
       fence_proxy_async();
@@ -516,9 +528,26 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
 
   p.out0 = (__nv_bfloat16*)g.dk; p.o0_sb = g.dk_sb; p.o0_ss = g.dk_ss; p.o0_sh = g.dk_sh;
   p.out1 = (__nv_bfloat16*)g.dv; p.o1_sb = g.dv_sb; p.o1_ss = g.dv_ss; p.o1_sh = g.dv_sh;
+  const bool dq_by_gemm = g.ds_scratch != nullptr && a.S % BT == 0;
+  p.ds_out = dq_by_gemm ? (__nv_bfloat16*)g.ds_scratch : nullptr;
   cudaError_t e = a.D == 64 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, grid, stream)
                             : launch_bwd<128, true>(tq, tk, tv, tdo, p, grid, stream);
   if (e != cudaSuccess) return e;
+  p.ds_out = nullptr;
+  if (dq_by_gemm) {
+    // dQ[b, h] = dS[b, h] (S x S, the scale already folded in) @ K[b, h] (S x D); with a causal
+    // mask the k loop of a query tile stops at its own diagonal (nothing was written beyond it)
+    GemmArgs m;
+    m.M = a.S; m.N = a.D; m.K = a.S;
+    m.A = g.ds_scratch; m.lda = a.S; m.a_mn_major = 0;
+    m.a_stride_inner = (int64_t)a.S * a.S; m.a_stride_outer = (int64_t)a.H * a.S * a.S;
+    m.B = a.k; m.ldb = a.k_ss; m.b_mn_major = 1;
+    m.b_stride_inner = a.k_sh; m.b_stride_outer = a.k_sb;
+    m.C = g.dq; m.ldc = g.dq_ss; m.c_stride_inner = g.dq_sh; m.c_stride_outer = g.dq_sb;
+    m.batch_inner = a.H; m.batch_outer = a.B;
+    m.causal_k = a.causal ? 1 : 0;
+    return gemm_bf16(m, stream);
+  }
 
   p.out0 = (__nv_bfloat16*)g.dq; p.o0_sb = g.dq_sb; p.o0_ss = g.dq_ss; p.o0_sh = g.dq_sh;
   p.out1 = nullptr; p.o1_sb = p.o1_ss = p.o1_sh = 0;

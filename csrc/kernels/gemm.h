@@ -52,6 +52,8 @@ struct GemmArgs {
   int64_t ld_aux = 0;
   int causal_tiles = 0;  // 1: skip output tiles strictly above the diagonal (n0 > m0 + BM - 1);
                          // 2: skip tiles strictly below (m0 > n0 + BN - 1)
+  int causal_k = 0;      // 1: the k loop of the output tile at row m0 stops at k = m0 + 128
+                         //    (A is lower block-triangular in 128-blocks: attention dS / P)
   // Optional scratch for split-K (fp32, device memory valid on `stream`).  When a long-K
   // product has too few output tiles to fill the chip (weight gradients: K = tokens), K is cut
   // into S slices that run as S batches into workspace[S][M][N], and a second kernel sums the

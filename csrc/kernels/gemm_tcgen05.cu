@@ -78,6 +78,7 @@ struct KernelParams {
   const __nv_bfloat16* aux_in;
   long long ld_aux;
   int causal_tiles;
+  int causal_k;
   int vec_ok;  // C / residual / aux rows allow 16-byte vector access
   int vec32_ok;  // ... and 32-byte (256-bit) access
   // all-gather of B fused into the kernel (g_world <= 1: off)
@@ -380,6 +381,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (p.causal_tiles == 2) return m0 > n0 + BN - 1;
     return false;
   };
+  // pipeline stages of the k loop for the tile at row m0 (shortened for block-triangular A)
+  auto tile_stages = [&](int m0) -> int {
+    if (!p.causal_k) return num_kb;
+    int k_end = m0 + BM;
+    if (k_end > p.K) k_end = p.K;
+    return (k_end + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
+  };
 
   if (warp_idx == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -394,7 +402,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int n0 = (t / p.tiles_m) * BN;
         if (tile_skipped(m0, n0)) continue;
         const int bi = b % p.batch_inner, bo = b / p.batch_inner;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int nkb = tile_stages(m0);
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag,
                                  &g_gemm_error, 1)) {
             ok = false;
@@ -466,7 +475,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int nkb = tile_stages(m0);
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), phase, abort_flag, &g_gemm_error,
                                  3)) {
             ok = false;
@@ -1029,6 +1039,7 @@ KernelParams make_params(const GemmArgs& a) {
   p.aux_out = (__nv_bfloat16*)a.aux_out;
   p.aux_in = (const __nv_bfloat16*)a.aux_in; p.ld_aux = a.ld_aux;
   p.causal_tiles = a.causal_tiles;
+  p.causal_k = a.causal_k;
   const int cvec = a.c_fp32 ? 4 : 8;
   bool v = aligned16(a.C) && (a.ldc % cvec == 0) && (a.c_stride_inner % cvec == 0) &&
            (a.c_stride_outer % cvec == 0);
@@ -1225,7 +1236,7 @@ TileChoice choose_tile(const GemmArgs& a, int K, long long batch, bool c_fp32, b
   struct Cand { int pair, bn; };
   const Cand cands[7] = {{1, 256}, {1, 192}, {1, 128}, {0, 256}, {0, 192}, {0, 128}, {0, 64}};
   const int sms = num_sms();
-  const bool pair_ok = pair_mode() != 0 && a.causal_tiles == 0 && a.M > BM;
+  const bool pair_ok = pair_mode() != 0 && a.causal_tiles == 0 && a.causal_k == 0 && a.M > BM;
   const int force = forced_bn();
   const int clusters = pair_ok ? pair_clusters<256>() : 0;
   TileChoice best;
@@ -1273,7 +1284,7 @@ int choose_split(const GemmArgs& a, TileChoice* slice_tile) {
   TileChoice whole = choose_tile(a, a.K, batch, a.c_fp32 != 0);
   *slice_tile = whole;
   if (batch != 1 || a.bias || a.act != GEMM_ACT_NONE || a.residual || a.aux_out || a.aux_in ||
-      a.causal_tiles || a.K < 2048 || getenv("LT_GEMM_NO_SPLIT"))
+      a.causal_tiles || a.causal_k || a.K < 2048 || getenv("LT_GEMM_NO_SPLIT"))
     return 1;
   int best_s = 1;
   double best_cost = whole.cost;
