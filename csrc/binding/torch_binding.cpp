@@ -593,10 +593,12 @@ std::vector<Tensor> flash_backward(const Tensor& q, const Tensor& k, const Tenso
   b.dk_sb = dk.stride(0); b.dk_ss = dk.stride(1); b.dk_sh = dk.stride(2);
   b.dv_sb = dv.stride(0); b.dv_ss = dv.stride(1); b.dv_sh = dv.stride(2);
   b.delta = delta.data_ptr<float>();
-  // scratch for the dS tiles (dQ = dS K as a GEMM); LT_FLASH_DQ_GEMM=0 keeps the third kernel
+  // scratch for the dS tiles (dQ = dS K as a GEMM).  Measured: worth it at head dim 128 (0.456
+  // vs 0.526 ms at B 4, S 2048, H 16), a wash at head dim 64 where writing and re-reading dS costs
+  // what the third kernel's recomputation costs.  LT_FLASH_DQ_GEMM=0 / 1 forces it off / on.
   Tensor ds;
-  static const bool dq_gemm = [] { const char* e = getenv("LT_FLASH_DQ_GEMM"); return !(e && e[0] == '0'); }();
-  if (dq_gemm && S % 128 == 0) {
+  static const int dq_gemm = [] { const char* e = getenv("LT_FLASH_DQ_GEMM"); return e ? (e[0] == '0' ? 0 : 2) : 1; }();
+  if ((dq_gemm == 2 || (dq_gemm == 1 && D == 128)) && S % 128 == 0) {
     ds = at::empty({B, H, S, S}, q.options());
     b.ds_scratch = ds.data_ptr();
   }
