@@ -452,7 +452,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------
-// Head dim 64, second generation.  Same data flow as above, rebuilt around what the first
+// Second generation (the default; 64.4 vs 77.0 us at B 8, S 1024, H 12, D 64 and 162 vs 181 us at
+// B 4, S 2048, H 16, D 128).  Same data flow as above, rebuilt around what the first
 // kernel's profile showed: it was bound by the instruction stream of its four softmax warps
 // (about 7 instructions per score at two warps per scheduler), not by the tensor cores.
 //   * eight softmax warps: warps w and w+4 share the TMEM lanes (query rows) of quadrant w&3
@@ -515,21 +516,25 @@ __device__ __forceinline__ void v2_chunk_exp_store(const uint32_t (&r)[32], floa
   }
 }
 
-struct Fwd64Smem {
+template <int D>
+struct Fwd2Smem {
+  static constexpr int DC = D / 64;                          // 64-wide head-dim chunks
+  static constexpr int TILE = DC * CHUNK_BYTES;              // one [128 x D] operand
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + CHUNK_BYTES;          // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * CHUNK_BYTES;      // 2 stages
-  static constexpr int OFF_P = OFF_V + 2 * CHUNK_BYTES;      // 128 x 128 bf16 = 2 chunks
+  static constexpr int OFF_K = OFF_Q + TILE;                 // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * TILE;             // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * TILE;             // 128 x 128 bf16 = 2 chunks
   static constexpr int OFF_BAR = OFF_P + 2 * CHUNK_BYTES;
-  static constexpr int TMEM_COLS = 256;                      // 128 scores + 64 output
+  static constexpr int TMEM_COLS = 256;                      // 128 scores + D output columns
   static constexpr int TOTAL = OFF_BAR + 256;
 };
 
-__global__ void __launch_bounds__(V2_THREADS, 2)
-flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using L = Fwd64Smem;
-  constexpr int D = 64;
+template <int D>
+__global__ void __launch_bounds__(V2_THREADS, (D == 64 ? 2 : 1))
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using L = Fwd2Smem<D>;
+  constexpr int DC = L::DC;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023) {
@@ -588,18 +593,26 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp_idx == 0) {
     if (lane == 0) {
       const uint32_t qb = smem_u32(q_full);
-      mbar_arrive_expect_tx(qb, CHUNK_BYTES);
-      tma_load_4d(smem_u32(smem + L::OFF_Q), &tm_q, qb, 0, q0, h, b);
+      mbar_arrive_expect_tx(qb, L::TILE);
+#pragma unroll
+      for (int c = 0; c < DC; ++c)
+        tma_load_4d(smem_u32(smem + L::OFF_Q + c * CHUNK_BYTES), &tm_q, qb, 64 * c, q0, h, b);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         if (!mbar_wait_bounded(smem_u32(&kv_empty[st]), ((j >> 1) & 1) ^ 1, abort_flag,
                                &g_attn_error, 51))
           break;
         const uint32_t kb = smem_u32(&k_full[st]), vb = smem_u32(&v_full[st]);
-        mbar_arrive_expect_tx(kb, CHUNK_BYTES);
-        tma_load_4d(smem_u32(smem + L::OFF_K + st * CHUNK_BYTES), &tm_k, kb, 0, j * BN, h, b);
-        mbar_arrive_expect_tx(vb, CHUNK_BYTES);
-        tma_load_4d(smem_u32(smem + L::OFF_V + st * CHUNK_BYTES), &tm_v, vb, 0, j * BN, h, b);
+        mbar_arrive_expect_tx(kb, L::TILE);
+#pragma unroll
+        for (int c = 0; c < DC; ++c)
+          tma_load_4d(smem_u32(smem + L::OFF_K + st * L::TILE + c * CHUNK_BYTES), &tm_k, kb, 64 * c,
+                      j * BN, h, b);
+        mbar_arrive_expect_tx(vb, L::TILE);
+#pragma unroll
+        for (int c = 0; c < DC; ++c)
+          tma_load_4d(smem_u32(smem + L::OFF_V + st * L::TILE + c * CHUNK_BYTES), &tm_v, vb, 64 * c,
+                      j * BN, h, b);
       }
     }
   } else if (warp_idx == 1) {
@@ -615,11 +628,16 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!mbar_wait_bounded(smem_u32(s_empty), (j & 1) ^ 1, abort_flag, &g_attn_error, 54))
           return false;
         tc_fence_after_sync();
-        const uint64_t qd = make_smem_desc_sw128(smem_u32(smem + L::OFF_Q), 16, 1024);
-        const uint64_t kd = make_smem_desc_sw128(smem_u32(smem + L::OFF_K + st * CHUNK_BYTES), 16, 1024);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_bf16(tmem_s, qd + (uint64_t)(ks * 2), kd + (uint64_t)(ks * 2), idesc_s, ks > 0 ? 1u : 0u);
+        for (int c = 0; c < DC; ++c) {
+          const uint64_t qd = make_smem_desc_sw128(smem_u32(smem + L::OFF_Q + c * CHUNK_BYTES), 16, 1024);
+          const uint64_t kd = make_smem_desc_sw128(
+              smem_u32(smem + L::OFF_K + st * L::TILE + c * CHUNK_BYTES), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(tmem_s, qd + (uint64_t)(ks * 2), kd + (uint64_t)(ks * 2), idesc_s,
+                      (c > 0 || ks > 0) ? 1u : 0u);
+        }
         umma_commit(smem_u32(s_full));
         return true;
       };
@@ -635,13 +653,13 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           break;
         }
         tc_fence_after_sync();
-        // O[128 x 64] (+)= P[128 x 128 keys] V[128 keys x 64]
+        // O[128 x D] (+)= P[128 x 128 keys] V[128 keys x D]
 #pragma unroll
         for (int kc = 0; kc < 2; ++kc) {
           const uint64_t pd = make_smem_desc_sw128(smem_u32(smem + L::OFF_P + kc * CHUNK_BYTES), 16, 1024);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * CHUNK_BYTES) + (kc * 64 + ks * 16) * 128;
+            const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * L::TILE) + (kc * 64 + ks * 16) * 128;
             const uint64_t vd = make_smem_desc_sw128(v_addr, CHUNK_BYTES, 1024);
             umma_bf16(tmem_o, pd + (uint64_t)(ks * 2), vd, idesc_o, (j > 0 || kc > 0 || ks > 0) ? 1u : 0u);
           }
@@ -712,12 +730,16 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
-          tmem_ld_32x32(tmem_o + lane_base + half * 32, ra);
-          tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
-          tmem_st_32x16(tmem_o + lane_base + half * 32, *reinterpret_cast<uint32_t(*)[16]>(&ra[0]));
-          tmem_st_32x16(tmem_o + lane_base + half * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&ra[16]));
+          for (int oc = 0; oc < D / 64; ++oc) {     // this thread's D/2 output columns, 32 at a time
+            const uint32_t o_addr = tmem_o + lane_base + half * (D / 2) + oc * 32;
+            tmem_ld_32x32(o_addr, ra);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
+            tmem_st_32x16(o_addr, *reinterpret_cast<uint32_t(*)[16]>(&ra[0]));
+            tmem_st_32x16(o_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(&ra[16]));
+          }
           tmem_st_wait();
           l2.x *= alpha;
           l2.y *= alpha;
@@ -744,27 +766,32 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         float* lsum = reinterpret_cast<float*>(smem + L::OFF_P);
         const float l_mine = l2.x + l2.y;
         lsum[half * 128 + row] = l_mine;
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_base + half * 32, r);
-        tmem_ld_wait();
         // all 256 threads meet on the (now unused) p_full barrier: a bounded wait, unlike bar.sync
         mbar_arrive(smem_u32(p_full));
         const bool met = mbar_wait_bounded_warp(smem_u32(p_full), n_kv & 1, abort_flag, &g_attn_error, 60);
         const float l = l_mine + lsum[(1 - half) * 128 + row];
-        if (met && qi < p.S) {
-          const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-          __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_ss +
-                                (long long)h * p.o_sh + half * 32;
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_ss +
+                              (long long)h * p.o_sh + half * (D / 2);
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 u;
-            __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&u);
+        for (int oc = 0; oc < D / 64; ++oc) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_base + half * (D / 2) + oc * 32, r);
+          tmem_ld_wait();
+          if (met && qi < p.S) {
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
-              hb[t] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * t]) * inv,
-                                            __uint_as_float(r[i + 2 * t + 1]) * inv);
-            *reinterpret_cast<uint4*>(orow + i) = u;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 u;
+              __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                hb[t] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * t]) * inv,
+                                              __uint_as_float(r[i + 2 * t + 1]) * inv);
+              *reinterpret_cast<uint4*>(orow + oc * 32 + i) = u;
+            }
           }
+        }
+        if (met && qi < p.S) {
           if (p.lse && half == 0)
             p.lse[((long long)b * p.H + h) * p.S + qi] =
                 (l > 0.0f) ? m_used * p.scale + __logf(l) : -INFINITY;
@@ -781,11 +808,12 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
 }
 
-cudaError_t launch_fwd64_v2(const AttnArgs& a, cudaStream_t stream) {
-  using L = Fwd64Smem;
+template <int D>
+cudaError_t launch_fwd_v2(const AttnArgs& a, cudaStream_t stream) {
+  using L = Fwd2Smem<D>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd64_kernel,
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd2_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return e;
     attr_set = true;
@@ -803,13 +831,13 @@ cudaError_t launch_fwd64_v2(const AttnArgs& a, cudaStream_t stream) {
   p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
   p.lse = a.lse;
   dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
-  cudaError_t le = launch_pdl(flash_fwd64_kernel, grid, dim3(V2_THREADS), L::TOTAL, stream, tq, tk, tv, p);
+  cudaError_t le = launch_pdl(flash_fwd2_kernel<D>, grid, dim3(V2_THREADS), L::TOTAL, stream, tq, tk, tv, p);
   if (le != cudaSuccess) return le;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
 
-// LT_FLASH_FWD_V1=1 selects the first-generation kernel for head dim 64 (comparison runs)
+// LT_FLASH_FWD_V1=1 selects the first-generation kernel (comparison runs)
 bool use_fwd_v1() {
   static int v = -1;
   if (v < 0) {
@@ -863,8 +891,8 @@ cudaError_t flash_attention_forward(const AttnArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
        reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.o)) & 15)
     return cudaErrorInvalidValue;
-  if (a.D == 64) return use_fwd_v1() ? launch_fwd<64>(a, stream) : launch_fwd64_v2(a, stream);
-  return launch_fwd<128>(a, stream);
+  if (a.D == 64) return use_fwd_v1() ? launch_fwd<64>(a, stream) : launch_fwd_v2<64>(a, stream);
+  return use_fwd_v1() ? launch_fwd<128>(a, stream) : launch_fwd_v2<128>(a, stream);
 }
 
 }  // namespace lt
