@@ -158,3 +158,57 @@ def test_gather_matmul_fused_allgather_gemm():
     comm.destroy()
     """)
 
+
+def test_rank_leaving_between_steps_is_seen_on_the_host_before_the_next_launch():
+    """Two GPU ranks train with the fused kernels; rank 1 then stops between steps with nothing
+    in flight.  Rank 0 learns of it from the heartbeat on the host and never launches the next
+    collective (no device-side fault or hang is involved; NVLS is off, plain peer loads)."""
+    _run("""
+    import time, torch, torch.distributed as dist
+    import luatorch_b200 as lf
+    from luatorch_b200.distributed import comm
+    from luatorch_b200.distributed.elastic import Heartbeat, RankFailure, StepFailed, run_step_guarded
+    comm.init()
+    r, w = comm.rank(), comm.world_size()
+    store = dist.distributed_c10d._get_default_store()
+    hb = Heartbeat(store, r, w, interval_s=0.05, stale_after_s=0.8)
+    lf.manual_seed(3)
+    model = lf.nn.Sequential(lf.nn.Linear(64, 128), lf.nn.GELU(), lf.nn.Linear(128, 16))
+    ddp = lf.distributed.DDP(model, mode="sharded", bucket_mb=0.02)
+    opt = lf.optim.AdamW(ddp.parameters(), 1e-2)
+    ddp.attach(opt)
+    crit = lf.nn.MSELoss()
+    x = lf.Tensor.wrap(torch.randn(32, 64, device="cuda"))
+    y = lf.Tensor.wrap(torch.randn(32, 16, device="cuda"))
+    launched = [0]
+    def step():
+        launched[0] += 1
+        lf.autograd.zero_graph(); ddp.zero_grad()
+        loss = crit(ddp(x), y)
+        lf.autograd.backward(loss)
+        ddp.sync_gradients(); opt.step()
+        torch.cuda.synchronize()
+        ddp.check()
+    for s_ in range(2):                       # both ranks present
+        run_step_guarded(step, s_, hb)
+    dist.barrier()
+    torch.cuda.synchronize()                  # nothing of this rank is in flight any more
+    if r == 1:
+        hb.stop()                             # the rank "leaves": its heartbeat stops
+        store.wait(["lt_test_done"])          # stay alive (and silent) until rank 0 has noticed
+    else:
+        t0, failed = time.time(), None
+        while time.time() - t0 < 15:
+            try:
+                run_step_guarded(lambda: None, 2, hb)   # the host check precedes every launch
+            except StepFailed as e:
+                failed = e
+                break
+            time.sleep(0.1)
+        assert failed is not None and isinstance(failed.cause, RankFailure) and failed.cause.ranks == [1]
+        assert launched[0] == 2               # no third step was launched
+        store.set("lt_test_done", "1")
+        print("CASE_OK")
+    hb.stop()
+    comm.destroy()
+    """)
