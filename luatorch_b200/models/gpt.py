@@ -99,7 +99,9 @@ class GPT(Module):
         top_k = top_k or 0
         was_training = self.training
         self.eval()
-        tokens = [int(v) for v in prompt._t.reshape(-1).tolist()]
+        # a Tensor of token ids (as in the reference) or any plain sequence of ints
+        src = prompt._t if isinstance(prompt, Tensor) else torch.as_tensor(prompt)
+        tokens = [int(v) for v in src.reshape(-1).tolist()]
         dev = self.token_emb.weight._t.device
         gen = B.cpu_generator()
         with autograd.no_grad():
