@@ -17,8 +17,6 @@ extern "C" void tensor_cuda_free(Tensor* t);
 
 namespace {
 
-struct ViewHeader { Tensor* source; };   // stored right after a view's Tensor struct
-
 size_t dtype_size(int dtype) {
   switch (dtype) {
     case DTYPE_FLOAT64: case DTYPE_INT64: return 8;
@@ -52,8 +50,8 @@ double next_unit() { return (double)(next_u64() >> 11) * (1.0 / 9007199254740992
 
 }  // namespace
 
-// Views are allocated as {Tensor, ViewHeader}; `grad == nullptr && strides` cannot tell them
-// apart, so the marker lives in the allocation itself: is_view() compares a magic word.
+// Every tensor is allocated as a block {Tensor, magic, source}: for a view, `magic` holds
+// kViewMagic and `source` the tensor whose storage it shares; is_view() compares the word.
 namespace {
 constexpr uint64_t kViewMagic = 0x4c54564945570001ull;
 struct ViewBlock { Tensor t; uint64_t magic; Tensor* source; };
