@@ -70,6 +70,18 @@ def _load():
     lib.tensor_flash_attention_cuda.argtypes = [TP, TP, TP, C.c_int, C.c_int, C.c_int, C.c_int]
     lib.tensor_sum_cuda.restype, lib.tensor_sum_cuda.argtypes = C.c_float, [TP]
     lib.pool_init.restype = None
+    lib.pool_clear.restype = None
+
+    def _non_null(name):
+        def check(result, func, args):
+            if not result:
+                raise RuntimeError("reference op %s returned NULL (it printed its own error above)" % name)
+            return result
+        return check
+
+    for n in unary + binary + ["tensor_new", "tensor_new_cuda", "tensor_reshape",
+                               "tensor_fused_layernorm_cuda", "tensor_flash_attention_cuda"]:
+        getattr(lib, n).errcheck = _non_null(n)
     lib.luatorch_nccl_init.restype, lib.luatorch_nccl_init.argtypes = C.c_int, [C.c_int]
     lib.luatorch_nccl_allreduce.restype = C.c_int
     lib.luatorch_nccl_allreduce.argtypes = [C.POINTER(C.c_void_p), C.c_int64, C.c_int]
@@ -362,7 +374,23 @@ def run(args, cfg):
     import random
     rng = random.Random(1234)
     tokens = [rng.randrange(cfg["vocab"]) for _ in range(cfg["micro_batch"] * cfg["seq"])]
-    reps = [Replica(lib, rt, d, cfg, tokens) for d in range(n)]
+    # The reference's memory pool is one list for all devices (csrc/cuda/memory_pool.cu:9-21,
+    # 46-68): a block freed on device 0 is handed to the next allocation on device 1, whose
+    # cudaMemset then fails with "invalid argument".  Its own pool_clear() between devices is
+    # the only way to drive several GPUs from its single process, so the harness calls it
+    # whenever it switches device (this serialises the devices, as the reference would).
+    def switch_device():
+        if n > 1:
+            lib.pool_clear()
+
+    reps = []
+    try:
+        for d in range(n):
+            switch_device()
+            reps.append(Replica(lib, rt, d, cfg, tokens))
+    except RuntimeError as e:
+        emit({"unavailable": "the reference library failed while building the model: %s" % str(e)[:200]})
+        return
     if n > 1:
         rc = lib.luatorch_nccl_init(n)
         if rc != 0:
@@ -371,6 +399,7 @@ def run(args, cfg):
 
     def step():
         for r in reps:
+            switch_device()
             r.forward_backward()
         if n > 1:   # one blocking collective per parameter, as ddp.lua:48-61 does
             lists = [r.grad_list() for r in reps]
@@ -386,6 +415,14 @@ def run(args, cfg):
             rt.cudaSetDevice(d)
             rt.cudaDeviceSynchronize()
 
+    try:
+        _timed_part(args, cfg, rt, lib, reps, n, step, sync, emit)
+    except RuntimeError as e:
+        emit({"unavailable": "the reference library failed on this configuration: %s" % str(e)[:200]})
+    return
+
+
+def _timed_part(args, cfg, rt, lib, reps, n, step, sync, emit):
     warmup, steps = max(3, args.warmup), args.steps
     # the reference's step is long; cap the step count so the arm finishes in minutes
     steps_run = steps
