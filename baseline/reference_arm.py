@@ -418,7 +418,14 @@ def run(args, cfg):
     try:
         _timed_part(args, cfg, rt, lib, reps, n, step, sync, emit)
     except RuntimeError as e:
-        emit({"unavailable": "the reference library failed on this configuration: %s" % str(e)[:200]})
+        why = str(e)[:160]
+        if n > 1:
+            # measured on 2 B200s: cuBLAS status 13 from tensor_matmul_cuda on device 1
+            why = ("the reference drives all GPUs from one process but keeps ONE cuBLAS handle, "
+                   "created on device 0 (csrc/cuda/ops/matmul.cu:21-35), and one memory pool for "
+                   "all devices (csrc/cuda/memory_pool.cu:9-21): its matmul fails on device 1 "
+                   "(cublas sgemm status 13), so it cannot run a GPU-resident step on %d GPUs; " % n + why)
+        emit({"unavailable": "the reference library failed on this configuration: " + why})
     return
 
 
