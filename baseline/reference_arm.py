@@ -383,6 +383,32 @@ def run(args, cfg):
         if n > 1:
             lib.pool_clear()
 
+    if n > 1:
+        # Probe before building n full replicas (minutes of host-side initialisation): one small
+        # matmul on device 1.  The reference's single cuBLAS handle lives on device 0.
+        try:
+            for dev in (0, 1):          # the handle is created by the first matmul, on device 0
+                rt.cudaSetDevice(dev)
+                lib.pool_clear()
+                sh = (C.c_int64 * 2)(64, 64)
+                a = lib.tensor_new(sh, 2, 0, 0)
+                b = lib.tensor_new(sh, 2, 0, 0)
+                lib.tensor_fill(a, 1.0)
+                lib.tensor_fill(b, 1.0)
+                lib.tensor_to_cuda(a)
+                lib.tensor_to_cuda(b)
+                c = lib.tensor_matmul_cuda(a, b)
+                rt.cudaDeviceSynchronize()
+                for t in (a, b, c):
+                    lib.tensor_free(t)
+            rt.cudaSetDevice(0)
+        except RuntimeError as e:
+            emit({"unavailable": "the reference drives all GPUs from one process but keeps ONE cuBLAS "
+                                 "handle, created on device 0 (csrc/cuda/ops/matmul.cu:21-35), and one "
+                                 "memory pool for all devices (csrc/cuda/memory_pool.cu:9-21): a matmul on "
+                                 "device 1 fails (%s), so it cannot run a GPU-resident step on %d GPUs"
+                                 % (str(e)[:80], n)})
+            return
     reps = []
     try:
         for d in range(n):
