@@ -385,7 +385,8 @@ def run(args, cfg):
 
     if n > 1:
         # Probe before building n full replicas (minutes of host-side initialisation): one small
-        # matmul on device 1.  The reference's single cuBLAS handle lives on device 0.
+        # matmul on device 0, which creates the reference's single cuBLAS handle there, then the
+        # same on device 1, where that handle returns an error status (no device fault).
         try:
             for dev in (0, 1):          # the handle is created by the first matmul, on device 0
                 rt.cudaSetDevice(dev)
