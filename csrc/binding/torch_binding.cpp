@@ -248,13 +248,23 @@ void fill_random(Tensor& out, int64_t seed, int64_t offset, bool normal) {
   check(lt::fill_random(dt(out), out.data_ptr(), out.numel(), (uint64_t)seed, (uint64_t)offset,
                         normal, cur_stream()), "fill_random");
 }
-Tensor dropout(const Tensor& x, double p, int64_t seed, int64_t offset) {
+// `dyn_offset`: optional int64[1] on the device, added to `offset` inside the kernel (graph replay)
+Tensor dropout_dyn(const Tensor& x, double p, int64_t seed, int64_t offset, const OptT& dyn_offset) {
   need_cuda_contig(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
+  const uint64_t* dyn = nullptr;
+  if (dyn_offset.has_value()) {
+    TORCH_CHECK(dyn_offset->is_cuda() && dyn_offset->scalar_type() == at::kLong &&
+                dyn_offset->numel() >= 1, "dyn_offset: int64 CUDA tensor expected");
+    dyn = reinterpret_cast<const uint64_t*>(dyn_offset->data_ptr<int64_t>());
+  }
   Tensor out = at::empty_like(x);
   check(lt::dropout(dt(x), x.data_ptr(), out.data_ptr(), x.numel(), (float)p, (uint64_t)seed,
-                    (uint64_t)offset, cur_stream()), "dropout");
+                    (uint64_t)offset, cur_stream(), dyn), "dropout");
   return out;
+}
+Tensor dropout(const Tensor& x, double p, int64_t seed, int64_t offset) {
+  return dropout_dyn(x, p, seed, offset, c10::nullopt);
 }
 std::vector<Tensor> split_bf16(const Tensor& a) {
   need_cuda_contig(a, "a");
@@ -508,9 +518,12 @@ Tensor relayout(const Tensor& in, int64_t batch, int64_t C, int64_t hw, bool to_
 }
 
 // ------------------------------------------------------------------------------ optimizers
-void adamw_flat(Tensor& master, const OptT& shadow, const Tensor& grad, Tensor& m, Tensor& v,
-                const OptT& seg_end, const OptT& seg_wd, double lr, double beta1, double beta2,
-                double eps, double bc1, double bc2, double grad_scale, const OptT& skip_flag) {
+// `dyn`: optional fp32[3] on the device holding {lr, bc1, bc2}; when given it replaces the
+// by-value scalars inside the kernel, so a captured graph can be replayed for later steps.
+void adamw_flat_dyn(Tensor& master, const OptT& shadow, const Tensor& grad, Tensor& m, Tensor& v,
+                    const OptT& seg_end, const OptT& seg_wd, double lr, double beta1, double beta2,
+                    double eps, double bc1, double bc2, double grad_scale, const OptT& skip_flag,
+                    const OptT& dyn) {
   need_cuda_contig(master, "master"); need_cuda_contig(grad, "grad");
   need_cuda_contig(m, "m"); need_cuda_contig(v, "v");
   TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
@@ -520,6 +533,11 @@ void adamw_flat(Tensor& master, const OptT& shadow, const Tensor& grad, Tensor& 
   lt::AdamArgs a{(float)lr, (float)beta1, (float)beta2, (float)eps, (float)bc1, (float)bc2,
                  (float)grad_scale,
                  skip_flag.has_value() ? skip_flag->data_ptr<int>() : nullptr};
+  if (dyn.has_value()) {
+    TORCH_CHECK(dyn->is_cuda() && dyn->scalar_type() == at::kFloat && dyn->numel() >= 3,
+                "dyn: fp32 CUDA tensor with {lr, bc1, bc2} expected");
+    a.dyn = dyn->data_ptr<float>();
+  }
   const int nseg = seg_end.has_value() ? (int)seg_end->numel() : 0;
   check(lt::adamw_flat(master.data_ptr<float>(), optptr(shadow) ? shadow->data_ptr() : nullptr,
                        grad.data_ptr(), dt(grad), m.data_ptr<float>(), v.data_ptr<float>(),
@@ -527,14 +545,47 @@ void adamw_flat(Tensor& master, const OptT& shadow, const Tensor& grad, Tensor& 
                        nseg ? seg_wd->data_ptr<float>() : nullptr, nseg, a, cur_stream()),
         "adamw_flat");
 }
-void sgd_flat(Tensor& master, const OptT& shadow, const Tensor& grad, const OptT& vel, double lr,
-              double momentum, bool nesterov, double grad_scale) {
+void adamw_flat(Tensor& master, const OptT& shadow, const Tensor& grad, Tensor& m, Tensor& v,
+                const OptT& seg_end, const OptT& seg_wd, double lr, double beta1, double beta2,
+                double eps, double bc1, double bc2, double grad_scale, const OptT& skip_flag) {
+  adamw_flat_dyn(master, shadow, grad, m, v, seg_end, seg_wd, lr, beta1, beta2, eps, bc1, bc2,
+                 grad_scale, skip_flag, c10::nullopt);
+}
+// Step-dependent scalars of a replayed graph: dyn fp32[>=3] <- {lr, bc1, bc2}, dyn_offset int64[1].
+void set_step_scalars(const OptT& dyn, double lr, double bc1, double bc2, const OptT& dyn_offset,
+                      int64_t offset) {
+  float* d = nullptr;
+  uint64_t* o = nullptr;
+  if (dyn.has_value()) {
+    TORCH_CHECK(dyn->is_cuda() && dyn->scalar_type() == at::kFloat && dyn->numel() >= 3);
+    d = dyn->data_ptr<float>();
+  }
+  if (dyn_offset.has_value()) {
+    TORCH_CHECK(dyn_offset->is_cuda() && dyn_offset->scalar_type() == at::kLong);
+    o = reinterpret_cast<uint64_t*>(dyn_offset->data_ptr<int64_t>());
+  }
+  if (!d && !o) return;
+  c10::cuda::CUDAGuard guard(dyn.has_value() ? dyn->device() : dyn_offset->device());
+  check(lt::set_step_scalars(d, (float)lr, (float)bc1, (float)bc2, o, (uint64_t)offset,
+                             cur_stream()), "set_step_scalars");
+}
+void sgd_flat_dyn(Tensor& master, const OptT& shadow, const Tensor& grad, const OptT& vel,
+                  double lr, double momentum, bool nesterov, double grad_scale, const OptT& dyn) {
   need_cuda_contig(master, "master"); need_cuda_contig(grad, "grad");
   c10::cuda::CUDAGuard guard(master.device());
+  const float* dyn_lr = nullptr;
+  if (dyn.has_value()) {
+    TORCH_CHECK(dyn->is_cuda() && dyn->scalar_type() == at::kFloat && dyn->numel() >= 1);
+    dyn_lr = dyn->data_ptr<float>();
+  }
   check(lt::sgd_flat(master.data_ptr<float>(), shadow.has_value() ? shadow->data_ptr() : nullptr,
                      grad.data_ptr(), dt(grad), vel.has_value() ? vel->data_ptr<float>() : nullptr,
                      master.numel(), (float)lr, (float)momentum, nesterov, (float)grad_scale,
-                     cur_stream()), "sgd_flat");
+                     cur_stream(), dyn_lr), "sgd_flat");
+}
+void sgd_flat(Tensor& master, const OptT& shadow, const Tensor& grad, const OptT& vel, double lr,
+              double momentum, bool nesterov, double grad_scale) {
+  sgd_flat_dyn(master, shadow, grad, vel, lr, momentum, nesterov, grad_scale, c10::nullopt);
 }
 
 // ------------------------------------------------------------------------------ attention
@@ -682,6 +733,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("transpose2d", &transpose2d);
   m.def("fill_random", &fill_random);
   m.def("dropout", &dropout);
+  m.def("dropout_dyn", &dropout_dyn);
+  m.def("set_pdl", [](int64_t v) { lt::set_pdl_override((int)v); });
   m.def("split_bf16", &split_bf16);
   m.def("reduce", &reduce);
   m.def("dot", &dot);
@@ -706,6 +759,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relayout", &relayout);
   m.def("adamw_flat", &adamw_flat);
   m.def("sgd_flat", &sgd_flat);
+  m.def("adamw_flat_dyn", &adamw_flat_dyn);
+  m.def("sgd_flat_dyn", &sgd_flat_dyn);
+  m.def("set_step_scalars", &set_step_scalars);
   m.def("flash_forward", &flash_forward);
   m.def("flash_backward", &flash_backward);
   m.def("attention_device_error", &attention_device_error);

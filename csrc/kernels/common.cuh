@@ -20,7 +20,7 @@ extern std::atomic<uint64_t> g_ops_launches;
 // and its writes are visible.  Rules: a kernel launched this way touches no global memory
 // before pdl_wait(), and pdl_trigger() (allow the NEXT kernel to be scheduled) may come first
 // because the next kernel waits for this one in the same way.  LT_PDL=0 in the environment
-// turns the launch attribute off (plain stream order).
+// turns the launch attribute off (plain stream order); set_pdl_override() does it at run time.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -31,7 +31,11 @@ __device__ __forceinline__ void pdl_enter() {
   pdl_wait();
 }
 
+// -1: follow LT_PDL; 0 / 1: forced off / on at run time (set_pdl_override in ops.h)
+extern int g_pdl_override;
+
 inline bool pdl_enabled() {
+  if (g_pdl_override >= 0) return g_pdl_override != 0;
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("LT_PDL");

@@ -14,6 +14,8 @@ namespace lt {
 
 std::atomic<uint64_t> g_ops_launches{0};
 uint64_t ops_launch_count() { return g_ops_launches.load(); }
+int g_pdl_override = -1;
+void set_pdl_override(int v) { g_pdl_override = v < 0 ? -1 : (v != 0); }
 
 namespace {
 
@@ -533,7 +535,8 @@ fill_random_kernel(T* __restrict__ out, int64_t n, uint64_t seed, uint64_t offse
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 dropout_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, float p, float inv_keep,
-               uint64_t seed, uint64_t offset) {
+               uint64_t seed, uint64_t offset, const uint64_t* __restrict__ dyn_offset) {
+  if (dyn_offset) offset += *dyn_offset;
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   const int64_t groups = (n + 3) / 4;
@@ -565,12 +568,12 @@ cudaError_t fill_random(int dtype, void* out, int64_t n, uint64_t seed, uint64_t
 }
 
 cudaError_t dropout(int dtype, const void* x, void* out, int64_t n, float p, uint64_t seed,
-                    uint64_t offset, cudaStream_t s) {
+                    uint64_t offset, cudaStream_t s, const uint64_t* dyn_offset) {
   if (n <= 0) return cudaSuccess;
   const float inv_keep = p < 1.0f ? 1.0f / (1.0f - p) : 0.0f;
   LT_DISPATCH_DTYPE(dtype, T, {
     dropout_kernel<T><<<stream_grid((n + 3) / 4, THREADS), THREADS, 0, s>>>(
-        (const T*)x, (T*)out, n, p, inv_keep, seed, offset);
+        (const T*)x, (T*)out, n, p, inv_keep, seed, offset, dyn_offset);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })

@@ -18,6 +18,8 @@ enum UnaryOp : int {
 enum ReduceOp : int { RED_SUM = 0, RED_MAX = 1, RED_MIN = 2 };
 
 uint64_t ops_launch_count();
+// Programmatic dependent launch at run time: 0 = off, 1 = on, -1 = follow LT_PDL (default).
+void set_pdl_override(int v);
 
 // ---- elementwise family (reference: csrc/cuda/ops/arithmetic.cu:57-143, activation.cu:25-60)
 cudaError_t binary_op(int op, int dtype, const void* a, const void* b, void* out, int64_t n,
@@ -44,8 +46,10 @@ cudaError_t transpose2d(int dtype, const void* in, void* out, int64_t rows, int6
 cudaError_t fill_random(int dtype, void* out, int64_t n, uint64_t seed, uint64_t offset,
                         int normal, cudaStream_t s);
 // out = x * mask / (1-p), mask ~ Bernoulli(1-p) regenerated from (seed, offset) in backward
+// `dyn_offset` (device, optional) is added to `offset` inside the kernel: a replayed CUDA graph
+// gets fresh masks by advancing that one word between replays.
 cudaError_t dropout(int dtype, const void* x, void* out, int64_t n, float p, uint64_t seed,
-                    uint64_t offset, cudaStream_t s);
+                    uint64_t offset, cudaStream_t s, const uint64_t* dyn_offset = nullptr);
 // fp32 a -> bf16 hi and lo parts (a ~= hi + lo) used by the fp32-accurate GEMM path
 cudaError_t split_bf16(const float* a, void* hi, void* lo, int64_t n, cudaStream_t s);
 
@@ -142,6 +146,9 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, bc1, bc2;
   float grad_scale;          // multiplied into the gradient before use (1/world, 1/loss-scale)
   const int* skip_flag;      // device flag: nonzero => leave everything untouched (overflow)
+  // device {lr, bc1, bc2}: when set, these replace the by-value fields, so that a captured
+  // CUDA graph can be replayed with the step-dependent scalars of each new step
+  const float* dyn = nullptr;
 };
 // Segment table: seg_end[i] = exclusive end element of segment i, seg_wd[i] = its weight decay.
 cudaError_t adamw_flat(float* master, void* shadow_bf16, const void* grad, int grad_dtype,
@@ -149,6 +156,11 @@ cudaError_t adamw_flat(float* master, void* shadow_bf16, const void* grad, int g
                        int nseg, AdamArgs args, cudaStream_t s);
 cudaError_t sgd_flat(float* master, void* shadow_bf16, const void* grad, int grad_dtype,
                      float* vel, int64_t n, float lr, float momentum, int nesterov,
-                     float grad_scale, cudaStream_t s);
+                     float grad_scale, cudaStream_t s, const float* dyn_lr = nullptr);
+// Writes the step-dependent scalars that a replayed CUDA graph reads from device memory:
+// dyn = {lr, bc1, bc2} (AdamArgs::dyn, sgd_flat's dyn_lr) and the dropout offset word.
+// Either pointer may be null.  One single-thread launch, ordered before the graph by the stream.
+cudaError_t set_step_scalars(float* dyn, float lr, float bc1, float bc2, uint64_t* dyn_offset,
+                             uint64_t offset, cudaStream_t s);
 
 }  // namespace lt

@@ -43,6 +43,14 @@ __device__ __forceinline__ int find_segment(const int64_t* seg_end, int nseg, in
   return lo;
 }
 
+__device__ __forceinline__ void apply_dyn(AdamArgs& a) {
+  if (a.dyn) {
+    a.lr = a.dyn[0];
+    a.bc1 = a.dyn[1];
+    a.bc2 = a.dyn[2];
+  }
+}
+
 __device__ __forceinline__ void adam_update(float& p, float g, float& m, float& v, float wd,
                                             const AdamArgs& a) {
   p *= 1.0f - a.lr * wd;
@@ -62,6 +70,7 @@ adamw_vec_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow,
                  int nseg, AdamArgs a) {
   pdl_enter();
   if (a.skip_flag && *a.skip_flag) return;
+  apply_dyn(a);
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = tid; i < n4; i += nthreads) {
@@ -91,6 +100,7 @@ adamw_scalar_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shad
                     int64_t n, const int64_t* __restrict__ seg_end,
                     const float* __restrict__ seg_wd, int nseg, AdamArgs a) {
   if (a.skip_flag && *a.skip_flag) return;
+  apply_dyn(a);
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = tid; i < n; i += nthreads) {
@@ -106,7 +116,8 @@ template <typename TG>
 __global__ void __launch_bounds__(THREADS)
 sgd_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow,
            const TG* __restrict__ grad, float* __restrict__ vel, int64_t n, float lr, float mu,
-           int nesterov, float gscale) {
+           int nesterov, float gscale, const float* __restrict__ dyn_lr) {
+  if (dyn_lr) lr = *dyn_lr;
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = tid; i < n; i += nthreads) {
@@ -124,7 +135,25 @@ sgd_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow,
   }
 }
 
+__global__ void set_step_scalars_kernel(float* dyn, float lr, float bc1, float bc2,
+                                        uint64_t* dyn_offset, uint64_t offset) {
+  if (threadIdx.x != 0) return;
+  if (dyn) {
+    dyn[0] = lr;
+    dyn[1] = bc1;
+    dyn[2] = bc2;
+  }
+  if (dyn_offset) *dyn_offset = offset;
+}
+
 }  // namespace
+
+cudaError_t set_step_scalars(float* dyn, float lr, float bc1, float bc2, uint64_t* dyn_offset,
+                             uint64_t offset, cudaStream_t s) {
+  set_step_scalars_kernel<<<1, 32, 0, s>>>(dyn, lr, bc1, bc2, dyn_offset, offset);
+  LT_COUNT_LAUNCH();
+  return cudaGetLastError();
+}
 
 cudaError_t adamw_flat(float* master, void* shadow, const void* grad, int grad_dtype, float* m,
                        float* v, int64_t n, const int64_t* seg_end, const float* seg_wd, int nseg,
@@ -160,16 +189,17 @@ cudaError_t adamw_flat(float* master, void* shadow, const void* grad, int grad_d
 
 cudaError_t sgd_flat(float* master, void* shadow, const void* grad, int grad_dtype, float* vel,
                      int64_t n, float lr, float momentum, int nesterov, float grad_scale,
-                     cudaStream_t s) {
+                     cudaStream_t s, const float* dyn_lr) {
   if (n <= 0) return cudaSuccess;
   const int grid = stream_grid(n, THREADS);
   if (grad_dtype == DT_F32)
     sgd_kernel<float><<<grid, THREADS, 0, s>>>(master, (__nv_bfloat16*)shadow, (const float*)grad,
-                                               vel, n, lr, momentum, nesterov, grad_scale);
+                                               vel, n, lr, momentum, nesterov, grad_scale,
+                                               dyn_lr);
   else if (grad_dtype == DT_BF16)
     sgd_kernel<__nv_bfloat16><<<grid, THREADS, 0, s>>>(master, (__nv_bfloat16*)shadow,
                                                        (const __nv_bfloat16*)grad, vel, n, lr,
-                                                       momentum, nesterov, grad_scale);
+                                                       momentum, nesterov, grad_scale, dyn_lr);
   else
     return cudaErrorInvalidValue;
   LT_COUNT_LAUNCH();

@@ -323,10 +323,20 @@ def column_sum(g: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: 
     return out
 
 
+# Set by luatorch_b200.cuda.graph.GraphedStep while it captures a training step: an object with
+# device tensors `dyn_opt` (fp32 {lr, bc1, bc2}) and `dyn_off` (int64 Philox offset).  Ops whose
+# launch arguments change from step to step read them from there instead, so that the captured
+# graph stays valid when it is replayed.
+_graph_capture = None
+
+
 def dropout(x: torch.Tensor, p: float) -> Tuple[torch.Tensor, object]:
     """Returns (y, ctx); ctx regenerates the same mask in `dropout_backward`."""
     if x.is_cuda:
         seed, off = next_philox(x.numel())
+        cap = _graph_capture
+        if cap is not None:
+            return ext().dropout_dyn(_k(x), p, seed, off, cap.dyn_off), (seed, off, cap.dyn_off)
         return ext().dropout(_k(x), p, seed, off), (seed, off)
     mask = (torch.rand(x.shape, generator=_cpu_gen) >= p).to(x.dtype) / (1.0 - p if p < 1 else 1.0)
     return x * mask, mask
@@ -334,6 +344,8 @@ def dropout(x: torch.Tensor, p: float) -> Tuple[torch.Tensor, object]:
 
 def dropout_backward(dy: torch.Tensor, p: float, ctx) -> torch.Tensor:
     if dy.is_cuda:
+        if len(ctx) == 3:
+            return ext().dropout_dyn(_k(dy), p, ctx[0], ctx[1], ctx[2])
         seed, off = ctx
         return ext().dropout(_k(dy), p, seed, off)
     return dy * ctx
@@ -566,8 +578,35 @@ def layernorm_backward(x, dy, gamma, mean, rstd, dgamma, dbeta, accumulate=False
     return dx.reshape(x.shape).to(x.dtype)
 
 
+def adamw_flat(master, shadow, grad, m, v, seg_end, seg_wd, lr, beta1, beta2, eps, bc1, bc2,
+               grad_scale, skip_flag) -> None:
+    """One launch over a flat arena (csrc/kernels/optim.cu).  Under graph capture lr and the
+    bias corrections are read from device memory."""
+    cap = _graph_capture
+    if cap is not None:
+        cap.uses_optimizer = True
+        ext().adamw_flat_dyn(master, shadow, grad, m, v, seg_end, seg_wd, lr, beta1, beta2, eps,
+                             bc1, bc2, grad_scale, skip_flag, cap.dyn_opt)
+    else:
+        ext().adamw_flat(master, shadow, grad, m, v, seg_end, seg_wd, lr, beta1, beta2, eps, bc1,
+                         bc2, grad_scale, skip_flag)
+
+
+def sgd_flat(master, shadow, grad, vel, lr, momentum, nesterov, grad_scale) -> None:
+    cap = _graph_capture
+    if cap is not None:
+        cap.uses_optimizer = True
+        ext().sgd_flat_dyn(master, shadow, grad, vel, lr, momentum, nesterov, grad_scale,
+                           cap.dyn_opt)
+    else:
+        ext().sgd_flat(master, shadow, grad, vel, lr, momentum, nesterov, grad_scale)
+
+
 def adam_step(p, g, m, v, lr, beta1, beta2, eps, bc1, bc2, wd):
     if p.is_cuda:
+        if _graph_capture is not None:
+            raise RuntimeError("graph capture needs the parameters in a flat arena "
+                               "(wrap the model in distributed.DDP before building the optimizer)")
         n = p.numel()
         ext().adamw_flat(p.view(-1), None, _k(g).view(-1), m.view(-1), v.view(-1),
                          torch.tensor([n], device=p.device, dtype=torch.int64),

@@ -204,11 +204,11 @@ class DDP:
                 bc1, bc2 = 1.0 - opt.beta1 ** t, 1.0 - opt.beta2 ** t
                 seg_end, seg_wd = opt.segments()
                 if self.world == 1:
-                    B.ext().adamw_flat(a.master[lo:hi], a.shadow[lo:hi], a.grad[lo:hi],
-                                       opt.m_flat[lo:hi], opt.v_flat[lo:hi],
-                                       (seg_end - lo).clamp_(min=0), seg_wd, opt.lr, opt.beta1,
-                                       opt.beta2, opt.epsilon, bc1, bc2, opt.grad_scale,
-                                       opt.skip_flag)
+                    B.adamw_flat(a.master[lo:hi], a.shadow[lo:hi], a.grad[lo:hi],
+                                 opt.m_flat[lo:hi], opt.v_flat[lo:hi],
+                                 (seg_end - lo).clamp_(min=0), seg_wd, opt.lr, opt.beta1,
+                                 opt.beta2, opt.epsilon, bc1, bc2, opt.grad_scale,
+                                 opt.skip_flag)
                 else:
                     B.ext().allreduce_adamw(
                         self.grad_buf.ptrs, self.grad_buf.signal_ptrs, self.rank, self.world, lo,

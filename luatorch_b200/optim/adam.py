@@ -94,9 +94,9 @@ class Adam:
             a = self.arena
             seg_end, seg_wd = self.segments()
             if a.master.is_cuda:
-                B.ext().adamw_flat(a.master, a.shadow, a.grad, self.m_flat, self.v_flat, seg_end,
-                                   seg_wd, self.lr, self.beta1, self.beta2, self.epsilon, bc1, bc2,
-                                   self.grad_scale, self.skip_flag)
+                B.adamw_flat(a.master, a.shadow, a.grad, self.m_flat, self.v_flat, seg_end,
+                             seg_wd, self.lr, self.beta1, self.beta2, self.epsilon, bc1, bc2,
+                             self.grad_scale, self.skip_flag)
                 return
         for i, u in enumerate(self.units):
             g = _unit_grad(u, self.params)

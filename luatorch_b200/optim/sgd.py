@@ -39,8 +39,8 @@ class SGD:
     def step(self) -> None:
         if self.arena is not None and self.arena.master.is_cuda:
             a = self.arena
-            B.ext().sgd_flat(a.master, a.shadow, a.grad, self.v_flat if self.momentum else None,
-                             self.lr, self.momentum, self.nesterov, self.grad_scale)
+            B.sgd_flat(a.master, a.shadow, a.grad, self.v_flat if self.momentum else None,
+                       self.lr, self.momentum, self.nesterov, self.grad_scale)
             return
         for i, u in enumerate(self.units):
             g = _unit_grad(u, self.params)

@@ -2,7 +2,8 @@
 synthetic inputs [batch 256, 784] uniform in [0,1], labels uniform in [0,10),
 Linear(784,256)-ReLU-Dropout(0.2)-Linear(256,10), cross entropy, Adam lr 1e-3, bf16 compute
 with fp32 master weights.  With more than one rank the whole model is one small gradient
-bucket, so this exercises the one-shot fused all-reduce + Adam kernel."""
+bucket, so this exercises the one-shot fused all-reduce + Adam kernel.  On one rank `--graph`
+replays the whole step as a CUDA graph (the step is launch-bound)."""
 from __future__ import annotations
 
 import argparse
@@ -18,6 +19,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--mode", default="replicated", choices=["replicated", "sharded", "nccl"])
+    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph (1 rank)")
     args = ap.parse_args(argv)
     lf.distributed.init()
     rank, world = lf.distributed.rank(), lf.distributed.world_size()
@@ -34,14 +36,21 @@ def main(argv=None):
     x = lf.Tensor.wrap(torch.rand(args.batch, 784, generator=g).to(dev))
     y = lf.Tensor.wrap(torch.randint(0, 10, (args.batch,), generator=g).float().to(dev))
     logger = lf.utils.Logger(max(1, args.steps // 5))
-    timer = StepTimer()
-    for step in range(args.steps):
+
+    def one_step():
         lf.autograd.zero_graph()
         ddp.zero_grad()
         loss = crit(ddp(x), y)
         lf.autograd.backward(loss)
         ddp.sync_gradients()
         opt.step()
+        return loss
+
+    if args.graph and cuda and world == 1:
+        one_step = lf.cuda.GraphedStep(one_step, opt, inputs=(x, y))
+    timer = StepTimer()
+    for step in range(args.steps):
+        loss = one_step()
         if (step + 1) % logger.print_every == 0 and rank == 0:
             logger.step = step
             logger.log(loss.item(), None, opt.lr)

@@ -92,3 +92,11 @@ def test_mlp_and_module_protocol():
     seq.zero_grad()
     assert all(p.grad is None for p in seq.parameters())
     assert lf.version == "0.1.0"
+
+
+def test_graphed_step_needs_a_gpu():
+    import pytest
+    if torch.cuda.is_available():
+        pytest.skip("CPU-only check")
+    with pytest.raises(RuntimeError):
+        lf.cuda.GraphedStep(lambda: None, optimizer=None)
