@@ -24,6 +24,7 @@ from LuaJIT (lua/luatorch/autograd.lua:52-93, lua/luatorch/optim/adam.lua:44-86)
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional, Sequence
 
 import torch
@@ -43,11 +44,14 @@ class GraphedStep:
                  batches into them.
     warmup    -- eager steps run before the capture (they are real training steps: kernels,
                  workspaces and allocator pools reach their steady state).
-    pdl       -- keep programmatic dependent launch on inside the captured graph.
+    pdl       -- keep programmatic dependent launch on inside the captured graph (default:
+                 off, or LT_GRAPH_PDL=1 in the environment).
     """
 
     def __init__(self, step_fn: Callable[[], object], optimizer, inputs: Sequence[Tensor] = (),
-                 warmup: int = 3, pdl: bool = False):
+                 warmup: int = 3, pdl: Optional[bool] = None):
+        if pdl is None:
+            pdl = os.environ.get("LT_GRAPH_PDL", "0") == "1"
         if not torch.cuda.is_available():
             raise RuntimeError("GraphedStep needs a CUDA device")
         from .. import distributed as dist_mod

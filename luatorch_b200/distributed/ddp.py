@@ -163,6 +163,7 @@ class DDP:
             self._launched[bi] = False
         self._cursor = 0
         self._synced = False
+        self._comm_used = False      # did this step put work on the communication stream?
 
     def _on_grad_ready(self, unit: Tensor) -> None:
         for bi in self._unit_bucket.get(id(unit), ()):
@@ -197,6 +198,7 @@ class DDP:
         ev = torch.cuda.Event()
         ev.record(cur)
         self._comm_stream.wait_event(ev)
+        self._comm_used = True
         with torch.cuda.stream(self._comm_stream):
             opt = self.optimizer
             if self._fusable() and (self.world == 1 or self.mode in ("sharded", "replicated")):
@@ -231,7 +233,9 @@ class DDP:
         if self._synced:
             return
         self._launch_ready(force=True)
-        if self.device == "cuda":
+        # join the communication stream only if this step forked onto it (a stream that did no
+        # work must not be waited on from a stream that is being captured into a graph)
+        if self.device == "cuda" and self._comm_used:
             ev = torch.cuda.Event()
             ev.record(self._comm_stream)
             torch.cuda.current_stream().wait_event(ev)

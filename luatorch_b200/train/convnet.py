@@ -43,6 +43,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--mode", default="sharded", choices=["replicated", "sharded", "nccl"])
+    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph (1 rank)")
     args = ap.parse_args(argv)
     lf.distributed.init()
     rank, world = lf.distributed.rank(), lf.distributed.world_size()
@@ -57,14 +58,21 @@ def main(argv=None):
     g = torch.Generator().manual_seed(200 + rank)
     x = lf.Tensor.wrap(torch.randn(args.batch * 3 * 32 * 32, generator=g).to(dev))
     y = lf.Tensor.wrap(torch.randint(0, 10, (args.batch,), generator=g).float().to(dev))
-    timer = StepTimer()
-    for step in range(args.steps):
+
+    def one_step():
         lf.autograd.zero_graph()
         ddp.zero_grad()
         loss = crit(model.forward(x, args.batch), y)
         lf.autograd.backward(loss)
         ddp.sync_gradients()
         opt.step()
+        return loss
+
+    if args.graph and cuda and world == 1:
+        one_step = lf.cuda.GraphedStep(one_step, opt, inputs=(x, y))
+    timer = StepTimer()
+    for step in range(args.steps):
+        loss = one_step()
         if rank == 0 and (step + 1) % max(1, args.steps // 5) == 0:
             print("step %5d  loss %.4f" % (step + 1, loss.item()), flush=True)
     ms = timer.elapsed_ms()

@@ -41,6 +41,8 @@ def main(argv=None):
     ap.add_argument("--max-steps", type=int, default=0)
     ap.add_argument("--out", default="", help="checkpoint path (.bin)")
     ap.add_argument("--bucket-mb", type=float, default=32.0)
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the step as a CUDA graph (one rank; two extra warm-up steps)")
     args = ap.parse_args(argv)
     cfg = lf.utils.Config({**DEFAULTS, **PRESETS[args.preset]})
     if args.config:
@@ -84,16 +86,25 @@ def main(argv=None):
             xt, yt = xt.pin_memory().to(dev, non_blocking=True), yt.pin_memory().to(dev, non_blocking=True)
         return lf.Tensor.wrap(xt.contiguous()), lf.Tensor.wrap(yt.contiguous())
 
-    timer = StepTimer()
-    window = 0
-    for step in range(1, cfg.get("max_steps") + 1):
-        x, y = batch()
+    x0, y0 = batch()
+
+    def one_step(x=x0, y=y0):
         lf.autograd.zero_graph()
         ddp.zero_grad()
         loss = crit(ddp(x), y)
         lf.autograd.backward(loss)
         ddp.sync_gradients()
         opt.step()
+        return loss
+
+    runner = None
+    if args.graph and cuda and world == 1:
+        runner = lf.cuda.GraphedStep(one_step, opt, inputs=(x0, y0), warmup=2)
+    timer = StepTimer()
+    window = 0
+    for step in range(1, cfg.get("max_steps") + 1):
+        x, y = batch()
+        loss = runner(x, y) if runner is not None else one_step(x, y)
         lr = sched.step()
         window += 1
         if step % cfg.get("print_every") == 0:

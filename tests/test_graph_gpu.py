@@ -136,3 +136,51 @@ def test_graphed_step_with_dropout_and_new_inputs():
     opt.set_lr(0.0)
     a, b = graphed().item(), graphed().item()
     assert a != b
+
+
+def _ddp_sgd(seed):
+    lf.manual_seed(seed)
+    model = nn.Sequential(nn.Linear(64, 128), nn.ReLU(), nn.Linear(128, 16))
+    ddp = lf.distributed.DDP(model)
+    opt = lf.optim.SGD(ddp.parameters(), 0.05, 0.9)
+    ddp.attach(opt)
+    g = torch.Generator().manual_seed(8)
+    x = T.wrap(torch.rand(128, 64, generator=g).cuda())
+    y = T.wrap(torch.randint(0, 16, (128,), generator=g).float().cuda())
+    crit = nn.CrossEntropyLoss()
+
+    def one_step():
+        ag.zero_graph()
+        ddp.zero_grad()
+        loss = crit(ddp(x), y)
+        ag.backward(loss)
+        ddp.sync_gradients()
+        opt.step()
+        return loss
+
+    return ddp, opt, one_step, (x, y)
+
+
+def test_graphed_step_with_ddp_wrapper_and_sgd():
+    # SGD is not fused into the gradient reduction, so at one rank the wrapper puts nothing on
+    # its communication stream; the capture must not wait on that idle stream
+    warm, steps = 2, 10
+    ddp_e, opt_e, step_e, _ = _ddp_sgd(51)
+    for k in range(warm + steps):
+        opt_e.set_lr(0.05 / (1 + k))
+        last_e = step_e().item()
+    ddp_g, opt_g, step_g, inputs = _ddp_sgd(51)
+    n = {"k": 0}
+
+    def warm_step():
+        if n["k"] < warm:
+            opt_g.set_lr(0.05 / (1 + n["k"]))
+        n["k"] += 1
+        return step_g()
+
+    graphed = lf.cuda.GraphedStep(warm_step, opt_g, inputs=inputs, warmup=warm)
+    for k in range(warm, warm + steps):
+        opt_g.set_lr(0.05 / (1 + k))
+        last_g = graphed().item()
+    assert abs(last_g - last_e) <= 1e-5 * max(1.0, abs(last_e)), (last_g, last_e)
+    torch.testing.assert_close(ddp_g.arena.master, ddp_e.arena.master, rtol=1e-5, atol=1e-7)
