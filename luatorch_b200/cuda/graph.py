@@ -64,7 +64,7 @@ class GraphedStep:
         self.step_fn = step_fn
         self.optimizer = optimizer
         self.inputs = list(inputs)
-        self.uses_optimizer = False
+        self.uses_optimizer = False     # set by the optimizer launch helpers during the capture
         dev = self.inputs[0]._t.device if self.inputs else torch.device("cuda")
         self.dyn_opt = torch.zeros(4, device=dev, dtype=torch.float32)
         self.dyn_off = torch.zeros(1, device=dev, dtype=torch.int64)
@@ -120,8 +120,8 @@ class GraphedStep:
                 dst._t.copy_(s, non_blocking=True)
         self._write_scalars()
         self.graph.replay()
-        if hasattr(self.optimizer, "t"):
-            self.optimizer.t += 1
+        if self.uses_optimizer and hasattr(self.optimizer, "t"):
+            self.optimizer.t += 1           # the replay ran one optimizer update
         self.replays += 1
         return self.output
 
