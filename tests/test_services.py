@@ -210,3 +210,19 @@ def test_arena_flat_optimizer_matches_per_tensor_optimizer():
     assert all(b1["start"] == b2["end"] for b1, b2 in zip(buckets, buckets[1:]))
     seg_end, seg_wd = ob.segments()
     assert int(seg_end[-1]) == arena.total and sorted(set(round(w, 6) for w in seg_wd.tolist())) == [0.0, 0.1]
+
+
+def test_xor_latency_benchmark_tool(tmp_path, capsys):
+    # examples/benchmark_pytorch.lua: per-step times, percentiles, predictions, CSV
+    from luatorch_b200.tools import xor_benchmark as xb
+    assert xb.percentile([5.0, 1.0, 3.0, 2.0, 4.0], 0.5) == 3.0
+    assert xb.percentile([5.0, 1.0, 3.0, 2.0, 4.0], 0.99) == 5.0
+    assert xb.percentile([7.0], 0.5) == 7.0
+    csv = tmp_path / "xor.csv"
+    ours, theirs = xb.main(["--steps", "400", "--csv", str(csv)])
+    out = capsys.readouterr().out
+    assert "median per step" in out and "predictions:" in out and "stock torch.nn" in out
+    assert ours["steps"] == 400 and ours["final_loss"] < 0.05 and theirs["final_loss"] < 0.05
+    assert ours["p50_ms"] <= ours["p95_ms"] <= ours["p99_ms"] <= ours["max_ms"]
+    lines = csv.read_text().strip().splitlines()
+    assert lines[0] == "step,time_ms,torch_time_ms" and len(lines) == 401
