@@ -10,7 +10,7 @@ import os
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB = os.path.join(ROOT, "luatorch_b200", "lib", "libluatorch.so")
+LIB = os.environ.get("LUATORCH_LIB") or os.path.join(ROOT, "luatorch_b200", "lib", "libluatorch.so")
 
 
 class CT(C.Structure):
