@@ -18,6 +18,11 @@ from ..tensor import Tensor
 
 
 class DataLoader:
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, data: Tensor, targets: Tensor, batch_size: int = 32, shuffle: bool = True,
                  rank: int = 0, world_size: int = 1, pin: bool = False):
         self.data = data

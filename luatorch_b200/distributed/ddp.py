@@ -40,6 +40,11 @@ from . import comm
 
 
 class DDP:
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, model, num_gpus: Optional[int] = None, bucket_mb: float = 32.0,
                  mode: str = "sharded", device: Optional[str] = None, max_blocks: int = 0,
                  broadcast_init: bool = True):

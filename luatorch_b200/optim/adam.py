@@ -38,6 +38,11 @@ def _unit_grad(u: Tensor, params: Sequence[Tensor]) -> Optional[torch.Tensor]:
 class Adam:
     decoupled = False
 
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, params: Sequence[Tensor], lr: float = None, beta1: float = None,
                  beta2: float = None, epsilon: float = None):
         self.params = list(params)

@@ -6,6 +6,11 @@ import math
 
 
 class CosineAnnealing:
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, optimizer, T_max: int, min_lr: float = 0.0):
         self.optimizer = optimizer
         self.T_max = T_max
@@ -35,6 +40,11 @@ class CosineAnnealing:
 
 
 class WarmupScheduler:
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, optimizer, warmup_steps: int, after_scheduler=None):
         self.optimizer = optimizer
         self.warmup_steps = warmup_steps
@@ -69,6 +79,11 @@ class WarmupScheduler:
 
 
 class StepLR:
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, optimizer, step_size: int, gamma: float = 0.1):
         self.optimizer = optimizer
         self.step_size = step_size

@@ -16,6 +16,11 @@ from .adam import _unit_grad
 
 
 class SGD:
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """`X.new(...)` is `X(...)`, the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def __init__(self, params: Sequence[Tensor], lr: float = None, momentum: float = None,
                  nesterov: bool = False):
         self.params = list(params)

@@ -226,3 +226,18 @@ def test_xor_latency_benchmark_tool(tmp_path, capsys):
     assert ours["p50_ms"] <= ours["p95_ms"] <= ours["p99_ms"] <= ours["max_ms"]
     lines = csv.read_text().strip().splitlines()
     assert lines[0] == "step,time_ms,torch_time_ms" and len(lines) == 401
+
+
+def test_reference_constructor_spelling():
+    # every class of the reference is built with X.new(...) (e.g. lua/luatorch/optim/adam.lua:22,
+    # lua/luatorch/data/dataloader.lua, lua/luatorch/distributed/ddp.lua)
+    p = [lf.Tensor.from_list([1.0, 2.0], [2])]
+    opt = lf.optim.Adam.new(p, 0.1)
+    assert isinstance(opt, lf.optim.Adam) and opt.lr == 0.1
+    assert isinstance(lf.optim.SGD.new(p, 0.1, 0.9), lf.optim.SGD)
+    assert isinstance(lf.optim.AdamW.new(p), lf.optim.AdamW)
+    assert isinstance(lf.optim.StepLR.new(opt, 2, 0.5), lf.optim.StepLR)
+    assert isinstance(lf.optim.CosineAnnealing.new(opt, 10), lf.optim.CosineAnnealing)
+    for cls in (lf.optim.WarmupScheduler, lf.data.DataLoader, lf.distributed.DDP, lf.utils.Logger,
+                lf.utils.Config, lf.cuda.GradScaler, lf.models.GPT, lf.models.MLP, lf.nn.Linear):
+        assert callable(getattr(cls, "new"))
