@@ -11,6 +11,9 @@
 //        tensor core as an MN-major operand).
 //   3. dQ kernel: one CTA per 128-query tile, loops over its key tiles, recomputes S / dP,
 //        dQ += dS K accumulates in TMEM.
+//      When the caller lends a dS scratch buffer (the default at head dim 128), launch 2
+//      also stores dS there and dQ = dS K runs as one batched GEMM that skips the key blocks
+//      above the causal diagonal (gemm_bf16 with causal_k) instead of launch 3.
 #include "attention.h"
 #include "sm100_ptx.cuh"
 #include "common.cuh"

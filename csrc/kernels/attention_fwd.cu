@@ -1,6 +1,8 @@
-// Causal / non-causal flash attention forward on tcgen05.
+// Causal / non-causal flash attention forward on tcgen05.  Two kernels: the first generation
+// described here (kept for comparison runs) and the second generation further down, which is
+// the default for head dims 64 and 128.
 //
-// One CTA per (128-query tile, head, batch); 192 threads:
+// First generation: one CTA per (128-query tile, head, batch); 192 threads:
 //   warp 0      TMA producer: Q once, then K/V tiles through a 2-stage ring
 //   warp 1      MMA issuer: S = Q K^T into one of two TMEM score buffers, O_tile = P V
 //   warps 2..5  softmax: thread r owns query row r; reads S from TMEM, keeps the running

@@ -2,12 +2,23 @@
 // CTA, operands staged in shared memory by TMA (128-byte swizzle), fp32 accumulators
 // in TMEM, epilogue read back with tcgen05.ld.
 //
-// Structure: persistent kernel, one CTA per SM, 192 threads:
-//   warp 0      TMA producer (one lane issues the tiled loads of each k-block)
-//   warp 1      TMEM owner + MMA issuer (one lane)
-//   warps 2..5  epilogue: each owns one 32-lane TMEM quadrant of the 128-row tile
+// Structure: persistent kernels, one CTA per SM, 64 + 32 * EPI_WARPS (= 320) threads:
+//   warp 0       TMA producer (one lane issues the tiled loads of each pipeline stage)
+//   warp 1       TMEM owner + MMA issuer (one lane)
+//   warps 2..9   epilogue: two warps per 32-lane TMEM quadrant of the 128-row tile, each
+//                taking half of the tile's columns
 // The TMEM accumulator is double buffered (2 x BN columns) so the epilogue of tile i
 // overlaps the main loop of tile i+1.
+//
+// Two kernels share that structure and the epilogue:
+//   gemm_tcgen05_kernel<BN>       one CTA per 128 x BN tile
+//   gemm_tcgen05_pair_kernel<BN>  a cluster of two CTAs (cta_group::2) per 256 x BN tile: each
+//                                 CTA loads its own 128 rows of A and half of B, the even CTA
+//                                 issues the MMAs for both, each CTA drains its own TMEM half
+// choose_tile() picks kernel and width from a cost model measured on the part; K may be split
+// into slices that run as batches into an fp32 workspace (choose_split, splitk_reduce_kernel);
+// the pair kernel can also pull remote row shards of B over NVLink while it multiplies the
+// local ones (GemmGather).  A SIMT kernel covers the shapes TMA cannot address.
 //
 // This kernel stands in for the reference's cublasSgemm / cublasSgemmStridedBatched
 // (csrc/cuda/ops/matmul.cu:121-133, 177-187) and for its add_broadcast / gelu_bias
