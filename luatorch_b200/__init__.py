@@ -33,6 +33,7 @@ from . import parallel  # noqa: E402
 from . import cuda  # noqa: E402
 from . import distributed  # noqa: E402
 from . import export  # noqa: E402
+from . import ops  # noqa: E402
 
 
 def launch_counts():
@@ -45,4 +46,4 @@ if _os.environ.get("LUAFLOW_DEBUG") or _os.environ.get("LUATORCH_DEBUG"):
     print("  gpus: %d" % distributed.num_gpus())
 
 __all__ = ["Tensor", "autograd", "nn", "optim", "data", "models", "io", "utils", "cuda",
-           "distributed", "export", "parallel", "manual_seed", "version", "launch_counts"]
+           "distributed", "export", "parallel", "ops", "manual_seed", "version", "launch_counts"]

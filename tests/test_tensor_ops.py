@@ -152,3 +152,32 @@ def test_fused_ops_have_cpu_paths():
     near(o.get(0), q.get(0), 1e-5)     # first causal row attends to itself only
     cols = T.im2col(T.new([1 * 1 * 3 * 3]).ones(), 1, 1, 3, 3, 2, 1, 0)
     assert cols.shape == [4, 4] and T.sum(cols) == 16
+
+
+def test_functional_ops_layer_on_cpu():
+    """lf.ops: the kernel-level functional surface, CPU path against torch."""
+    import torch
+    import luatorch_b200 as lf
+    ops = lf.ops
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(6, 16, generator=g)
+    gamma, beta = torch.rand(16, generator=g) + 0.5, torch.randn(16, generator=g)
+    y, mean, rstd = ops.layernorm(x, gamma, beta, 1e-5)
+    torch.testing.assert_close(y, torch.nn.functional.layer_norm(x, (16,), gamma, beta, 1e-5),
+                               rtol=1e-5, atol=1e-5)
+    bias = torch.randn(16, generator=g)
+    torch.testing.assert_close(ops.gelu_bias(x, bias),
+                               torch.nn.functional.gelu(x + bias, approximate="tanh"), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(ops.softmax(x), torch.softmax(x, -1))
+    labels = torch.randint(0, 16, (6,), generator=g).float()
+    loss = ops.cross_entropy(x, labels)
+    torch.testing.assert_close(loss.reshape(()), torch.nn.functional.cross_entropy(x, labels.long()))
+    dl = ops.cross_entropy_backward(x, labels)
+    xr = x.clone().requires_grad_(True)
+    torch.nn.functional.cross_entropy(xr, labels.long()).backward()
+    torch.testing.assert_close(dl, xr.grad, rtol=1e-5, atol=1e-6)
+    a, b = torch.randn(5, 7, generator=g), torch.randn(7, 3, generator=g)
+    torch.testing.assert_close(ops.matmul(a, b), a @ b)
+    torch.testing.assert_close(ops.column_sum(a), a.sum(0))
+    for name in ops.__all__:
+        assert callable(getattr(ops, name)), name
