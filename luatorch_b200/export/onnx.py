@@ -6,7 +6,9 @@ file size and first byte (:244-268).  Here `export(model, dummy_input, path)` em
 operator graph of the supported modules (Linear -> MatMul+Add, activations, LayerNorm,
 Dropout as Identity, Embedding -> Gather, Sequential / MLP chains, GPT with decomposed
 attention), ir_version 7 / opset 13 / producer "luatorch" as in the reference, and
-`verify(path)` parses the file back and checks its structure.
+`verify(path)` parses the file back and checks its structure; `run(path, input)` evaluates the
+stored graph with numpy (every operator the exporter emits), so an export can be checked
+numerically against the model it came from without an ONNX runtime: `verify(path, model, x)`.
 """
 from __future__ import annotations
 
@@ -306,7 +308,106 @@ def inspect(path: str) -> Dict:
     return info
 
 
-def verify(path: str) -> bool:
+def _signed(v: int) -> int:
+    return v - (1 << 64) if v >= 1 << 63 else v
+
+
+def load_graph(path: str) -> Dict:
+    """Full parse: {"nodes": [(op, inputs, outputs, attrs)], "initializers": {name: ndarray},
+    "input": name, "output": name}."""
+    with open(path, "rb") as f:
+        buf = f.read()
+    graph = next(v for field, wire, v in _fields(buf) if field == 7 and wire == 2)
+    nodes, inits, g_in, g_out = [], {}, None, None
+    for f2, w2, v2 in _fields(graph):
+        if f2 == 1:
+            ins, outs, op, attrs = [], [], None, {}
+            for ff, ww, x in _fields(v2):
+                if ff == 1:
+                    ins.append(x.decode())
+                elif ff == 2:
+                    outs.append(x.decode())
+                elif ff == 4:
+                    op = x.decode()
+                elif ff == 5:
+                    name, val, ints = None, None, []
+                    for fa, wa, xa in _fields(x):
+                        if fa == 1:
+                            name = xa.decode()
+                        elif fa == 2:
+                            val = struct.unpack("<f", xa)[0]
+                        elif fa == 3:
+                            val = _signed(xa)
+                        elif fa == 8:
+                            ints.append(_signed(xa))
+                    attrs[name] = ints if ints else val
+            nodes.append((op, ins, outs, attrs))
+        elif f2 == 5:
+            dims, dtype, name, raw = [], FLOAT, None, b""
+            for ff, ww, x in _fields(v2):
+                if ff == 1:
+                    dims.append(x)
+                elif ff == 2:
+                    dtype = x
+                elif ff == 8:
+                    name = x.decode()
+                elif ff == 9:
+                    raw = x
+            inits[name] = np.frombuffer(raw, dtype="<i8" if dtype == INT64 else "<f4").reshape(dims)
+        elif f2 in (11, 12):
+            nm = next(x.decode() for ff, ww, x in _fields(v2) if ff == 1)
+            if f2 == 11:
+                g_in = nm
+            else:
+                g_out = nm
+    return {"nodes": nodes, "initializers": inits, "input": g_in, "output": g_out}
+
+
+def _softmax(x: np.ndarray, axis: int) -> np.ndarray:
+    e = np.exp(x - x.max(axis=axis, keepdims=True))
+    return e / e.sum(axis=axis, keepdims=True)
+
+
+_NUMPY_OPS = {
+    "MatMul": lambda a, i: np.matmul(i[0], i[1]),
+    "Add": lambda a, i: i[0] + i[1],
+    "Sub": lambda a, i: i[0] - i[1],
+    "Mul": lambda a, i: i[0] * i[1],
+    "Div": lambda a, i: i[0] / i[1],
+    "Sqrt": lambda a, i: np.sqrt(i[0]),
+    "Relu": lambda a, i: np.maximum(i[0], 0),
+    "Sigmoid": lambda a, i: 1.0 / (1.0 + np.exp(-i[0])),
+    "Tanh": lambda a, i: np.tanh(i[0]),
+    "Identity": lambda a, i: i[0],
+    "ReduceMean": lambda a, i: i[0].mean(axis=tuple(a["axes"]), keepdims=bool(a.get("keepdims", 1))),
+    "Gather": lambda a, i: np.take(i[0], i[1].astype(np.int64), axis=a.get("axis", 0)),
+    "Reshape": lambda a, i: i[0].reshape([int(d) for d in i[1]]),
+    "Transpose": lambda a, i: np.transpose(i[0], a["perm"]),
+    "Softmax": lambda a, i: _softmax(i[0], a.get("axis", -1)),
+    "Cast": lambda a, i: i[0].astype(np.int64 if a["to"] == INT64 else np.float32),
+}
+
+
+def run(path: str, input) -> np.ndarray:
+    """Evaluate an exported file on `input` (Tensor, torch tensor or array) with numpy."""
+    g = load_graph(path)
+    if isinstance(input, Tensor):
+        input = input._t
+    if hasattr(input, "detach"):
+        input = input.detach().float().cpu().numpy()
+    env = dict(g["initializers"])
+    env[g["input"]] = np.asarray(input, dtype=np.float32)
+    for op, ins, outs, attrs in g["nodes"]:
+        fn = _NUMPY_OPS.get(op)
+        if fn is None:
+            raise NotImplementedError("onnx run: operator %s" % op)
+        env[outs[0]] = fn(attrs, [env[n] for n in ins])
+    return env[g["output"]]
+
+
+def verify(path: str, model=None, dummy_input=None, tol: float = 1e-4) -> bool:
+    """Structure check; with `model` and `dummy_input` also a numeric check of the stored graph
+    (numpy evaluation) against the model's own forward."""
     try:
         info = inspect(path)
     except Exception as e:
@@ -314,6 +415,14 @@ def verify(path: str) -> bool:
         return False
     ok = (info["ir_version"] == 7 and info["opset"] == 13 and info["producer"] == "luatorch"
           and len(info["ops"]) > 0 and len(info["inputs"]) == 1 and len(info["outputs"]) == 1)
+    if ok and model is not None and dummy_input is not None:
+        with autograd.no_grad():
+            want = model(dummy_input)
+        want = (want[0] if isinstance(want, tuple) else want)._t.detach().float().cpu().numpy()
+        got = run(path, dummy_input).reshape(want.shape)
+        err = float(np.abs(got - want).max())
+        ok = err <= tol * max(1.0, float(np.abs(want).max()))
+        print("onnx numeric check: max abs error %.3g (%s)" % (err, "ok" if ok else "MISMATCH"))
     print("onnx file %s: %s (%d nodes, %d initializers)" % (
         path, "valid" if ok else "INVALID", len(info["ops"]), len(info["initializers"])))
     return ok

@@ -177,6 +177,38 @@ def test_onnx_export_real_graph(tmp_path):
     assert not lf.export.onnx.verify(p)
 
 
+def test_onnx_export_is_numerically_the_model(tmp_path):
+    """The stored graph, evaluated with numpy, reproduces the model's forward."""
+    import torch
+    onnx, nn = lf.export.onnx, lf.nn
+    lf.manual_seed(12)
+    for pos in ("learned", "sinusoidal"):
+        gpt = lf.models.GPT(50, 32, 4, 2, 16, 0.0, pos=pos)
+        gpt.eval()
+        x = T.wrap(torch.randint(0, 50, (2, 8), generator=torch.Generator().manual_seed(1)).float())
+        p = str(tmp_path / ("gpt_%s.onnx" % pos))
+        onnx.export(gpt, x, p)
+        assert onnx.verify(p, gpt, x)
+        g = onnx.load_graph(p)
+        assert g["input"] == "input_1" and g["output"] == "output_1"
+        assert any(op == "Softmax" and attrs.get("axis") == -1 for op, _, _, attrs in g["nodes"])
+    seq = nn.Sequential(nn.Linear(6, 12), nn.GELU(), nn.LayerNorm(12), nn.Linear(12, 8), nn.BatchNorm1d(8),
+                        nn.SiLU(), nn.Linear(8, 3), nn.Sigmoid(), nn.Dropout(0.5), nn.Tanh())
+    x = T.wrap(torch.randn(16, 6, generator=torch.Generator().manual_seed(2)))
+    for _ in range(3):
+        seq(x)                                     # BatchNorm running statistics
+    seq.eval()
+    p = str(tmp_path / "seq.onnx")
+    onnx.export(seq, x, p)
+    assert onnx.verify(p, seq, x)
+    # a different model must fail the numeric check against the same file
+    lf.manual_seed(13)
+    other = nn.Sequential(nn.Linear(6, 12), nn.GELU(), nn.LayerNorm(12), nn.Linear(12, 8), nn.BatchNorm1d(8),
+                          nn.SiLU(), nn.Linear(8, 3), nn.Sigmoid(), nn.Dropout(0.5), nn.Tanh())
+    other.eval()
+    assert not onnx.verify(p, other, x)
+
+
 def test_arena_flat_optimizer_matches_per_tensor_optimizer():
     def build():
         lf.manual_seed(9)
