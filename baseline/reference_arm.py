@@ -26,8 +26,6 @@ from __future__ import annotations
 import ctypes as C
 import json
 import os
-import sys
-import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "_ref", "libluatorch.so")

@@ -18,7 +18,7 @@ import torch
 
 from .. import _backend as B
 from .. import autograd
-from ..parallel.arena import ParamArena, arena_of, storage_units
+from ..parallel.arena import ParamArena
 from ..tensor import Tensor
 
 

@@ -33,7 +33,6 @@ import torch
 import torch.distributed as dist
 
 from .. import _backend as B
-from .. import autograd
 from ..parallel.arena import ParamArena
 from ..tensor import Tensor
 from . import comm

@@ -26,7 +26,7 @@ from __future__ import annotations
 import json
 import os
 import struct
-from typing import List, Optional, Sequence
+from typing import List, Optional
 
 import numpy as np
 import torch

@@ -13,7 +13,7 @@ import torch
 from .. import _backend as B
 from .. import autograd
 from ..tensor import Tensor
-from .module import Module, compute_view, param
+from .module import Module, param
 
 
 def embedding_backward_into(weight_p: Tensor, dy: torch.Tensor, ids: torch.Tensor):

@@ -3,7 +3,6 @@
 reference module walks elements in Lua and never calls its own fused kernel."""
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

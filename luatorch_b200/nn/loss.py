@@ -7,7 +7,6 @@ entropy is the fused softmax-CE pair: forward saves the row log-sum-exp, backwar
 logits once and may overwrite them with the gradient."""
 from __future__ import annotations
 
-import torch
 
 from .. import _backend as B
 from .. import autograd

@@ -11,7 +11,7 @@ once per parameter on CUDA and runs 11 tensor ops with 8 temporaries per paramet
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

@@ -17,9 +17,8 @@ Differences from the reference that are deliberate:
 """
 from __future__ import annotations
 
-import math
 import sys
-from typing import Iterable, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 

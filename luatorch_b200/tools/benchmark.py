@@ -17,7 +17,6 @@ import argparse
 import json
 import math
 import os
-import sys
 
 import torch
 
@@ -63,7 +62,6 @@ def main(argv=None):
     ap.add_argument("--csv", default="")
     ap.add_argument("--shape", default="", help="gemm only: M,N,K override")
     args = ap.parse_args(argv)
-    import luatorch_b200 as lf
     from luatorch_b200 import _backend as B
     C = B.ext()
     hbm, tc, src = peaks()

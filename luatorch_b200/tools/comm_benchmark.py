@@ -20,7 +20,6 @@ from __future__ import annotations
 
 import json
 import os
-import sys
 
 import torch
 import torch.distributed as dist
@@ -30,7 +29,6 @@ NVLINK_BPS = 770e9
 
 
 def main():
-    import luatorch_b200 as lf
     from luatorch_b200 import _backend as B
     from luatorch_b200.distributed import comm
     comm.init()

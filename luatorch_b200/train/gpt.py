@@ -13,7 +13,6 @@ the device with CUDA events.
 from __future__ import annotations
 
 import argparse
-import os
 
 import torch
 

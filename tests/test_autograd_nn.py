@@ -2,7 +2,6 @@
 (test/test_autograd.lua:11-113, test/test_nn.lua:18-127, test/test_optim.lua:17-84,
 test/test_training.lua:11-104) plus gradient checks of every layer against torch.autograd."""
 import math
-import os
 
 import pytest
 import torch

@@ -1,6 +1,5 @@
 """Model-level GPU checks: the bf16 tensor-core path of each model family against the same
 model evaluated in fp32 on the CPU path (which test_autograd_nn.py pins to torch.autograd)."""
-import copy
 
 import pytest
 import torch

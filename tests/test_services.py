@@ -4,7 +4,6 @@ loading, tokenizer file format, logger CSV, config parsing, ONNX export, paramet
 optimizer equivalence."""
 import io
 import json
-import math
 import os
 import struct
 
