@@ -175,6 +175,86 @@ def test_cpu_ops_known_values(lib):
     assert cols.contents.shape[0] == 4 and cols.contents.shape[1] == 4 and L.tensor_sum(cols) == 16
 
 
+def _from_np(L, arr):
+    import numpy as np
+    arr = np.ascontiguousarray(arr, dtype=np.float32)
+    t = new(L, list(arr.shape))
+    C.memmove(t.contents.data, arr.ctypes.data, arr.nbytes)
+    return t
+
+
+def _to_np(L, t):
+    import numpy as np
+    assert t, "op returned NULL"
+    shape = [t.contents.shape[i] for i in range(t.contents.ndim)]
+    out = np.empty(shape, dtype=np.float32)
+    C.memmove(out.ctypes.data, t.contents.data, out.nbytes)
+    return out
+
+
+def test_cpu_ops_match_numpy_on_random_shapes(lib):
+    """Every CPU op of the C ABI against numpy, over random 1-d / 2-d / 3-d shapes."""
+    import numpy as np
+    L = lib
+    rng = np.random.default_rng(17)
+    gelu = lambda x: 0.5 * x * (1 + np.tanh(0.7978845608 * (x + 0.044715 * x ** 3)))
+    unary = {"tensor_neg": np.negative, "tensor_abs": np.abs, "tensor_exp": np.exp,
+             "tensor_relu": lambda x: np.maximum(x, 0), "tensor_sigmoid": lambda x: 1 / (1 + np.exp(-x)),
+             "tensor_tanh": np.tanh, "tensor_gelu": gelu, "tensor_silu": lambda x: x / (1 + np.exp(-x)),
+             "tensor_sqrt": lambda x: np.sqrt(np.abs(x)), "tensor_log": lambda x: np.log(np.abs(x) + 1)}
+    binary = {"tensor_add": np.add, "tensor_sub": np.subtract, "tensor_mul": np.multiply}
+    for trial in range(12):
+        shape = [int(d) for d in rng.integers(1, 9, size=int(rng.integers(1, 4)))]
+        a, b = rng.standard_normal(shape).astype(np.float32), rng.standard_normal(shape).astype(np.float32)
+        ta, tb = _from_np(L, a), _from_np(L, b)
+        for name, fn in unary.items():
+            src = a
+            if name == "tensor_sqrt":
+                src = np.abs(a)
+            elif name == "tensor_log":
+                src = np.abs(a) + 1
+            t = _from_np(L, src)
+            want = fn(a) if name not in ("tensor_sqrt", "tensor_log") else (np.sqrt(src) if name == "tensor_sqrt" else np.log(src))
+            np.testing.assert_allclose(_to_np(L, getattr(L, name)(t)), want, rtol=2e-5, atol=2e-6, err_msg=name)
+            L.tensor_free(t)
+        for name, fn in binary.items():
+            np.testing.assert_allclose(_to_np(L, getattr(L, name)(ta, tb)), fn(a, b), rtol=1e-6, atol=1e-6, err_msg=name)
+        np.testing.assert_allclose(_to_np(L, L.tensor_div(ta, _from_np(L, np.abs(b) + 0.5))), a / (np.abs(b) + 0.5), rtol=1e-5)
+        np.testing.assert_allclose(_to_np(L, L.tensor_mul_scalar(ta, 2.5)), a * 2.5, rtol=1e-6)
+        np.testing.assert_allclose(_to_np(L, L.tensor_add_scalar(ta, -1.25)), a - 1.25, rtol=1e-6, atol=1e-6)
+        np.testing.assert_allclose(_to_np(L, L.tensor_pow_scalar(_from_np(L, np.abs(a) + 0.1), 1.5)), (np.abs(a) + 0.1) ** 1.5, rtol=1e-5)
+        np.testing.assert_array_equal(_to_np(L, L.tensor_gt_scalar(ta, 0.1)), (a > 0.1).astype(np.float32))
+        assert abs(L.tensor_sum(ta) - float(a.sum())) < 1e-3 and abs(L.tensor_mean(ta) - float(a.mean())) < 1e-4
+        assert L.tensor_max(ta) == float(a.max()) and L.tensor_min(ta) == float(a.min())
+        assert abs(L.tensor_get(L.tensor_mse_loss(ta, tb), 0) - float(((a - b) ** 2).mean())) < 1e-4
+        assert abs(L.tensor_get(L.tensor_mae_loss(ta, tb), 0) - float(np.abs(a - b).mean())) < 1e-4
+        np.testing.assert_allclose(_to_np(L, L.tensor_mse_loss_backward(ta, tb)), 2 * (a - b) / a.size, rtol=1e-5, atol=1e-7)
+        # 2-d family
+        m, k, n = (int(d) for d in rng.integers(1, 12, size=3))
+        x, w, bias = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+        tx, tw = _from_np(L, x), _from_np(L, w)
+        y = _to_np(L, L.tensor_matmul(tx, tw))
+        np.testing.assert_allclose(y, x @ w, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(_to_np(L, L.tensor_transpose(tx)), x.T)
+        np.testing.assert_allclose(_to_np(L, L.tensor_add_broadcast(_from_np(L, y), _from_np(L, bias))), y + bias, rtol=1e-6, atol=1e-6)
+        np.testing.assert_allclose(_to_np(L, L.tensor_add_broadcast_backward(tx)), x.sum(0), rtol=1e-5, atol=1e-5)
+        e = np.exp(x - x.max(1, keepdims=True))
+        np.testing.assert_allclose(_to_np(L, L.tensor_softmax(tx)), e / e.sum(1, keepdims=True), rtol=1e-5, atol=1e-7)
+        labels = rng.integers(0, k, size=m)
+        lse = np.log(e.sum(1)) + x.max(1)
+        want = float((lse - x[np.arange(m), labels]).mean())
+        tl = _from_np(L, labels.astype(np.float32))
+        assert abs(L.tensor_get(L.tensor_cross_entropy_loss(tx, tl), 0) - want) < 1e-4
+        p = e / e.sum(1, keepdims=True)
+        p[np.arange(m), labels] -= 1
+        np.testing.assert_allclose(_to_np(L, L.tensor_cross_entropy_loss_backward(tx, tl)), p / m, rtol=1e-4, atol=1e-6)
+        nb = int(rng.integers(1, 4))
+        xa, xb = rng.standard_normal((nb, m, k)).astype(np.float32), rng.standard_normal((nb, k, n)).astype(np.float32)
+        np.testing.assert_allclose(_to_np(L, L.tensor_bmm(_from_np(L, xa), _from_np(L, xb))), xa @ xb, rtol=1e-4, atol=1e-5)
+        va, vb = rng.standard_normal(k).astype(np.float32), rng.standard_normal(k).astype(np.float32)
+        assert abs(L.tensor_dot(_from_np(L, va), _from_np(L, vb)) - float(va @ vb)) < 1e-4
+
+
 @pytest.mark.gpu
 def test_gpu_ops_match_cpu_ops(lib):
     import random
