@@ -96,7 +96,11 @@ int luatorch_nccl_init(int num_gpus) {
       (void)cudaGetLastError();
     }
     DevState& s = g_dev[d];
-    cudaError_t e = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking);
+    // A blocking stream: it is ordered after work already queued on the device's legacy default
+    // stream, where every tensor_*_cuda op of this library runs, so a collective never reads a
+    // buffer whose producing kernel is still running (the reference creates its streams the
+    // same way, csrc/distributed/nccl_wrapper.cu:62-65).
+    cudaError_t e = cudaStreamCreate(&s.stream);
     if (e != cudaSuccess) return fail("stream create", e);
     if (cudaMalloc(&s.pad, 1024) != cudaSuccess || cudaMalloc(&s.status, 64) != cudaSuccess ||
         cudaMalloc(&s.ptr_table, kMax * 8) != cudaSuccess || cudaMalloc(&s.pad_table, kMax * 8) != cudaSuccess)
@@ -126,6 +130,10 @@ int luatorch_nccl_allreduce(float** ptrs, int64_t count, int num_gpus) {
   for (int d = 1; d < num_gpus; ++d) same = same && ptrs[d] == ptrs[0];
   if (same) return 0;                     // the average of n copies of x is x
   if (!g_peer_ok) return host_staged_allreduce(ptrs, count, num_gpus);
+  // the peer kernel moves 16-byte vectors: a float* that is not 16-byte aligned takes the
+  // host-staged path instead of raising a misaligned-address error on the device
+  for (int d = 0; d < num_gpus; ++d)
+    if ((uintptr_t)ptrs[d] & 15) return host_staged_allreduce(ptrs, count, num_gpus);
   const int64_t gran = 4 * (int64_t)num_gpus;
   const int64_t main = count / gran * gran;
   uint64_t table[kMax];

@@ -662,25 +662,35 @@ int64_t attention_device_error() { return lt::attention_last_device_error(); }
 // Pointer tables are int64 CUDA tensors holding peer-mapped device addresses.
 void allreduce_adamw(const Tensor& grad_ptrs, const Tensor& signal_ptrs, int64_t rank,
                      int64_t world, int64_t elem_offset, int64_t n, Tensor& master,
-                     const OptT& shadow_ptrs, Tensor& m, Tensor& v, const OptT& seg_end,
+                     const OptT& shadow_ptrs, const OptT& m, const OptT& v, const OptT& seg_end,
                      const OptT& seg_wd, double lr, double beta1, double beta2, double eps,
                      double bc1, double bc2, double grad_scale, int64_t epoch, int64_t mode,
-                     int64_t max_blocks, Tensor& status) {
+                     int64_t max_blocks, Tensor& status, int64_t state_base, int64_t opt_kind,
+                     double momentum, bool nesterov, int64_t grad_mc, int64_t shadow_mc,
+                     const OptT& skip_flag, const OptT& dyn) {
   c10::cuda::CUDAGuard guard(master.device());
   lt::CommAdamArgs a;
   a.grad_ptrs = (const uint64_t*)grad_ptrs.data_ptr<int64_t>();
   a.signal_ptrs = (const uint64_t*)signal_ptrs.data_ptr<int64_t>();
   a.shadow_ptrs = shadow_ptrs.has_value() ? (const uint64_t*)shadow_ptrs->data_ptr<int64_t>()
                                           : nullptr;
+  a.grad_mc = reinterpret_cast<const void*>(grad_mc);
+  a.shadow_mc = reinterpret_cast<void*>(shadow_mc);
   a.rank = (int)rank; a.world = (int)world;
   a.elem_offset = elem_offset; a.n = n;
-  a.master = master.data_ptr<float>(); a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>();
+  a.master = master.data_ptr<float>();
+  a.m = m.has_value() ? m->data_ptr<float>() : nullptr;
+  a.v = v.has_value() ? v->data_ptr<float>() : nullptr;
+  a.state_base = state_base;
+  a.opt_kind = (int)opt_kind; a.momentum = (float)momentum; a.nesterov = nesterov ? 1 : 0;
   const int nseg = seg_end.has_value() ? (int)seg_end->numel() : 0;
   a.seg_end = nseg ? seg_end->data_ptr<int64_t>() : nullptr;
   a.seg_wd = nseg ? seg_wd->data_ptr<float>() : nullptr;
   a.nseg = nseg;
   a.adam = lt::AdamArgs{(float)lr, (float)beta1, (float)beta2, (float)eps, (float)bc1, (float)bc2,
-                        (float)grad_scale, nullptr};
+                        (float)grad_scale,
+                        skip_flag.has_value() ? skip_flag->data_ptr<int>() : nullptr,
+                        dyn.has_value() ? dyn->data_ptr<float>() : nullptr};
   a.epoch = (uint32_t)epoch; a.mode = (int)mode; a.max_blocks = (int)max_blocks;
   a.status = status.data_ptr<int>();
   check(lt::allreduce_adamw(a, cur_stream()), "allreduce_adamw");

@@ -11,6 +11,15 @@
 //                   peer is still reading this rank's buffers or writing into them.
 // All waits are bounded by a cycle budget; expiry is reported through `status`, never by a
 // trap or an endless spin.
+//
+// Epochs: a caller may pass the collective's sequence number, or 0 to let the kernel number
+// itself from a counter word in its own signal pad (the last block advances it), so that a
+// captured CUDA graph can be replayed: no launch argument changes from step to step.
+//
+// NVLS: when the caller passes multicast addresses of the gradient and shadow arenas, the
+// sharded kernel reads its slice with multimem.ld_reduce (the NVSwitch adds the ranks'
+// values and returns one vector) and publishes the updated weights with multimem.st (one
+// store, delivered to every rank), which halves the bytes each GPU moves over its links.
 #include "comm_kernels.h"
 
 #include <cuda_bf16.h>
@@ -28,6 +37,7 @@ constexpr int MAX_WORLD = 16;
 constexpr int SLOT_START = 0;
 constexpr int SLOT_DONE = 16;
 constexpr int SLOT_TICKET = 32;
+constexpr int SLOT_EPOCH = 33;        // local sequence counter for self-numbered collectives
 constexpr long long DEFAULT_BUDGET = 6000000000ll;  // about three seconds of SM clocks
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -48,6 +58,22 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
 __device__ __forceinline__ void st_peer16(void* p, uint4 v) {
   asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x),
                "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Sum over all ranks of 8 bf16 values at a multicast address (fp32 accumulation in the switch).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+// One 16-byte store delivered to the same offset of every rank's buffer.
+__device__ __forceinline__ void multimem_st16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
+               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
 
@@ -95,6 +121,16 @@ __device__ bool wait_peers(const uint32_t* my_pad, int base, int world, int rank
   return *sh_fail == 0;
 }
 
+// Sequence number of this collective: the caller's, or (caller passed 0) one more than the
+// counter word of this rank's own pad.  Every block reads the word before any block can
+// advance it (the advance happens after the last block has taken its ticket).
+__device__ __forceinline__ uint32_t resolve_epoch(const uint64_t* signal_ptrs, int rank,
+                                                  uint32_t epoch_arg) {
+  if (epoch_arg) return epoch_arg;
+  const volatile uint32_t* my_pad = reinterpret_cast<const volatile uint32_t*>(signal_ptrs[rank]);
+  return my_pad[SLOT_EPOCH] + 1u;
+}
+
 __device__ bool start_barrier(const uint64_t* signal_ptrs, int rank, int world, uint32_t epoch,
                               long long budget, int* status, int* sh_fail) {
   if (blockIdx.x == 0 && (int)threadIdx.x < world) {
@@ -108,7 +144,8 @@ __device__ bool start_barrier(const uint64_t* signal_ptrs, int rank, int world, 
 
 // Called by every block after its data phase. Only the last block talks to the peers.
 __device__ void done_barrier(const uint64_t* signal_ptrs, int rank, int world, uint32_t epoch,
-                             long long budget, int* status, int* sh_fail) {
+                             long long budget, int* status, int* sh_fail,
+                             bool self_numbered = false) {
   __threadfence_system();
   __syncthreads();
   __shared__ int is_last;
@@ -116,7 +153,10 @@ __device__ void done_barrier(const uint64_t* signal_ptrs, int rank, int world, u
   if (threadIdx.x == 0) {
     const unsigned t = atomicAdd(my_pad + SLOT_TICKET, 1u);
     is_last = (t == gridDim.x - 1);
-    if (is_last) my_pad[SLOT_TICKET] = 0;
+    if (is_last) {
+      my_pad[SLOT_TICKET] = 0;
+      if (self_numbered) my_pad[SLOT_EPOCH] = epoch;
+    }
   }
   __syncthreads();
   if (!is_last) return;
@@ -188,15 +228,47 @@ __device__ __forceinline__ void adam8(float* master, float* m, float* v, long lo
   *reinterpret_cast<float4*>(v + e + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
 }
 
+// SGD with momentum on 8 consecutive parameters (lua/luatorch/optim/sgd.lua:33-56 in the
+// reference): v = mu v + g; p -= lr v, or with Nesterov p -= lr (mu v + g).
+__device__ __forceinline__ void sgd8(float* master, float* vel, long long e, const float (&g)[8],
+                                     float lr, float mu, int nesterov, float gscale,
+                                     float (&p_out)[8]) {
+  float4 p0 = *reinterpret_cast<const float4*>(master + e), p1 = *reinterpret_cast<const float4*>(master + e + 4);
+  float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+  if (vel) {
+    float4 v0 = *reinterpret_cast<const float4*>(vel + e), v1 = *reinterpret_cast<const float4*>(vel + e + 4);
+    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * gscale;
+      vv[j] = mu * vv[j] + gj;
+      p[j] -= lr * (nesterov ? mu * vv[j] + gj : vv[j]);
+    }
+    *reinterpret_cast<float4*>(vel + e) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    *reinterpret_cast<float4*>(vel + e + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] -= lr * g[j] * gscale;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) p_out[j] = p[j];
+  *reinterpret_cast<float4*>(master + e) = make_float4(p[0], p[1], p[2], p[3]);
+  *reinterpret_cast<float4*>(master + e + 4) = make_float4(p[4], p[5], p[6], p[7]);
+}
+
 struct KArgs {
   const uint64_t* grad_ptrs;
   const uint64_t* signal_ptrs;
   const uint64_t* shadow_ptrs;
+  const __nv_bfloat16* grad_mc;   // multicast address of the gradient arena, or null
+  __nv_bfloat16* shadow_mc;       // multicast address of the shadow arena, or null
   int rank, world;
   long long elem_offset, n;
+  long long state_base;           // index into master / m / v of this rank's first element
   float* master; float* m; float* v;
   const int64_t* seg_end; const float* seg_wd; int nseg;
   AdamArgs adam;
+  int opt_kind; float momentum; int nesterov;
   uint32_t epoch;
   int mode;
   long long budget;
@@ -213,57 +285,81 @@ allreduce_adamw_kernel(const KArgs k) {
     sh_grad[threadIdx.x] = k.grad_ptrs[threadIdx.x];
     sh_shadow[threadIdx.x] = k.shadow_ptrs ? k.shadow_ptrs[threadIdx.x] : 0;
   }
-  if (!start_barrier(k.signal_ptrs, k.rank, world, k.epoch, k.budget, k.status, &sh_fail)) return;
+  const uint32_t epoch = resolve_epoch(k.signal_ptrs, k.rank, k.epoch);
+  if (!start_barrier(k.signal_ptrs, k.rank, world, epoch, k.budget, k.status, &sh_fail)) return;
+
+  AdamArgs adam = k.adam;
+  if (adam.dyn) { adam.lr = adam.dyn[0]; adam.bc1 = adam.dyn[1]; adam.bc2 = adam.dyn[2]; }
+  // an overflow flag must read the same on every rank (it is set from all-reduced data)
+  const bool skip = adam.skip_flag && *adam.skip_flag;
 
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const bool sharded = k.mode == COMM_TWO_SHOT_SHARDED;
+  const bool nvls = sharded && k.grad_mc != nullptr;
   const long long span = sharded ? k.n / world : k.n;
   const long long base = k.elem_offset + (sharded ? (long long)k.rank * span : 0);
-  for (long long i = tid; i < span / 8; i += nthreads) {
-    const long long e = base + i * 8;
-    const Adam8State st = adam8_load(k.master, k.m, k.v, e);   // HBM reads go out first
-    uint4 part[WORLD ? WORLD : MAX_WORLD];
-#pragma unroll
-    for (int q = 0; q < (WORLD ? WORLD : MAX_WORLD); ++q) {
-      if (q < world) {
-        const int src = (k.rank + q) % world;  // spread the first touch over the links
-        part[q] = ld_peer16(reinterpret_cast<const __nv_bfloat16*>(sh_grad[src]) + e);
-      }
-    }
+  for (long long i = skip ? span : tid; i < span / 8; i += nthreads) {
+    const long long e = base + i * 8;          // arena coordinate (gradients, shadow, segments)
+    const long long es = k.state_base + i * 8; // optimizer-state coordinate
+    Adam8State st;
+    if (k.opt_kind == COMM_OPT_ADAMW) st = adam8_load(k.master, k.m, k.v, es);  // HBM reads go out first
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    // fixed summation order (rank 0 .. world-1) so every rank computes identical bits
-#pragma unroll
-    for (int r = 0; r < (WORLD ? WORLD : MAX_WORLD); ++r) {
-      if (r < world) {
-        const int q = (r - k.rank + world) % world;
-        acc_bf16x8(part[q], g);
-      }
-    }
-    const float wd = k.nseg > 0 ? k.seg_wd[find_segment(k.seg_end, k.nseg, e)] : 0.0f;
-    float p[8];
-    adam8(k.master, k.m, k.v, e, st, g, wd, k.adam, p);
-    const uint4 packed = pack_bf16x8(p);
-    if (sharded) {
+    if (nvls) {
+      const uint4 r = multimem_ld_reduce_bf16x8(k.grad_mc + e);
+      acc_bf16x8(r, g);
+    } else {
+      uint4 part[WORLD ? WORLD : MAX_WORLD];
 #pragma unroll
       for (int q = 0; q < (WORLD ? WORLD : MAX_WORLD); ++q) {
-        if (q < world && sh_shadow[q]) {
-          const int dst = (k.rank + q) % world;
-          st_peer16(reinterpret_cast<__nv_bfloat16*>(sh_shadow[dst]) + e, packed);
+        if (q < world) {
+          const int src = (k.rank + q) % world;  // spread the first touch over the links
+          part[q] = ld_peer16(reinterpret_cast<const __nv_bfloat16*>(sh_grad[src]) + e);
+        }
+      }
+      // fixed summation order (rank 0 .. world-1) so every rank computes identical bits
+#pragma unroll
+      for (int r = 0; r < (WORLD ? WORLD : MAX_WORLD); ++r) {
+        if (r < world) {
+          const int q = (r - k.rank + world) % world;
+          acc_bf16x8(part[q], g);
+        }
+      }
+    }
+    float p[8];
+    if (k.opt_kind == COMM_OPT_ADAMW) {
+      const float wd = k.nseg > 0 ? k.seg_wd[find_segment(k.seg_end, k.nseg, e)] : 0.0f;
+      adam8(k.master, k.m, k.v, es, st, g, wd, adam, p);
+    } else {
+      sgd8(k.master, k.m, es, g, adam.lr, k.momentum, k.nesterov, adam.grad_scale, p);
+    }
+    const uint4 packed = pack_bf16x8(p);
+    if (sharded) {
+      if (nvls && k.shadow_mc) {
+        multimem_st16(k.shadow_mc + e, packed);
+      } else {
+#pragma unroll
+        for (int q = 0; q < (WORLD ? WORLD : MAX_WORLD); ++q) {
+          if (q < world) {
+            const int dst = (k.rank + q) % world;
+            if (sh_shadow[dst])
+              st_peer16(reinterpret_cast<__nv_bfloat16*>(sh_shadow[dst]) + e, packed);
+          }
         }
       }
     } else if (sh_shadow[k.rank]) {
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(sh_shadow[k.rank]) + e) = packed;
     }
   }
-  done_barrier(k.signal_ptrs, k.rank, world, k.epoch, k.budget, k.status, &sh_fail);
+  done_barrier(k.signal_ptrs, k.rank, world, epoch, k.budget, k.status, &sh_fail, k.epoch == 0);
 }
 
 __global__ void __launch_bounds__(THREADS)
 peer_broadcast_kernel(const uint64_t* buf_ptrs, const uint64_t* signal_ptrs, int rank, int world,
-                      int root, long long byte_offset, long long nbytes, uint32_t epoch,
+                      int root, long long byte_offset, long long nbytes, uint32_t epoch_arg,
                       long long budget, int* status) {
   __shared__ int sh_fail;
+  const uint32_t epoch = resolve_epoch(signal_ptrs, rank, epoch_arg);
   if (!start_barrier(signal_ptrs, rank, world, epoch, budget, status, &sh_fail)) return;
   if (rank != root) {
     const char* src = reinterpret_cast<const char*>(buf_ptrs[root]) + byte_offset;
@@ -280,17 +376,18 @@ peer_broadcast_kernel(const uint64_t* buf_ptrs, const uint64_t* signal_ptrs, int
     for (long long i = done + tid; i < nbytes; i += nthreads)
       dst[i] = *reinterpret_cast<const volatile char*>(src + i);
   }
-  done_barrier(signal_ptrs, rank, world, epoch, budget, status, &sh_fail);
+  done_barrier(signal_ptrs, rank, world, epoch, budget, status, &sh_fail, epoch_arg == 0);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 peer_allreduce_kernel(const uint64_t* buf_ptrs, const uint64_t* signal_ptrs, int rank, int world,
-                      long long elem_offset, long long n, float scale, uint32_t epoch,
+                      long long elem_offset, long long n, float scale, uint32_t epoch_arg,
                       long long budget, int* status) {
   __shared__ int sh_fail;
   __shared__ uint64_t sh_buf[MAX_WORLD];
   if ((int)threadIdx.x < world) sh_buf[threadIdx.x] = buf_ptrs[threadIdx.x];
+  const uint32_t epoch = resolve_epoch(signal_ptrs, rank, epoch_arg);
   if (!start_barrier(signal_ptrs, rank, world, epoch, budget, status, &sh_fail)) return;
   constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector
   const long long span = n / world;
@@ -323,7 +420,7 @@ peer_allreduce_kernel(const uint64_t* buf_ptrs, const uint64_t* signal_ptrs, int
       st_peer16(reinterpret_cast<T*>(sh_buf[dst]) + e, out);
     }
   }
-  done_barrier(signal_ptrs, rank, world, epoch, budget, status, &sh_fail);
+  done_barrier(signal_ptrs, rank, world, epoch, budget, status, &sh_fail, epoch_arg == 0);
 }
 
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t expected, long long budget,
@@ -357,9 +454,20 @@ cudaError_t allreduce_adamw(const CommAdamArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   KArgs k;
   k.grad_ptrs = a.grad_ptrs; k.signal_ptrs = a.signal_ptrs; k.shadow_ptrs = a.shadow_ptrs;
+  k.grad_mc = a.mode == COMM_TWO_SHOT_SHARDED ? reinterpret_cast<const __nv_bfloat16*>(a.grad_mc) : nullptr;
+  k.shadow_mc = reinterpret_cast<__nv_bfloat16*>(a.shadow_mc);
   k.rank = a.rank; k.world = a.world;
   k.elem_offset = a.elem_offset; k.n = a.n;
   k.master = a.master; k.m = a.m; k.v = a.v;
+  k.opt_kind = a.opt_kind; k.momentum = a.momentum; k.nesterov = a.nesterov;
+  if (a.opt_kind != COMM_OPT_ADAMW && a.opt_kind != COMM_OPT_SGD) return cudaErrorInvalidValue;
+  if (a.opt_kind == COMM_OPT_ADAMW && (!a.m || !a.v)) return cudaErrorInvalidValue;
+  {
+    const long long own = a.mode == COMM_TWO_SHOT_SHARDED ? a.n / a.world : a.n;
+    const long long first = a.elem_offset + (a.mode == COMM_TWO_SHOT_SHARDED ? (long long)a.rank * own : 0);
+    k.state_base = a.state_base >= 0 ? a.state_base : first;
+    if (k.state_base % 4 != 0) return cudaErrorInvalidValue;
+  }
   k.seg_end = a.seg_end; k.seg_wd = a.seg_wd; k.nseg = a.nseg;
   k.adam = a.adam; k.epoch = a.epoch; k.mode = a.mode;
   k.budget = DEFAULT_BUDGET; k.status = a.status;

@@ -7,8 +7,11 @@
 //
 // Every rank passes the same tables of peer-mapped addresses (one entry per rank, entry
 // `rank` being its own local buffer) and a signal pad per rank: uint32 slots
-// [0, world) "start" and [world, 2*world) "done", written by peers with release.sys stores
-// and read with acquire.sys loads.  `epoch` increases by one per collective on every rank.
+// [0, 16) "start" and [16, 32) "done", written by peers with release.sys stores and read with
+// acquire.sys loads, word 32 a block ticket, word 33 the pad's own collective counter.
+// `epoch` increases by one per collective on every rank; a caller that passes 0 lets the
+// kernels count for themselves in word 33 (all collectives on one pad must then do so, and
+// must be ordered on one stream), which is what makes a captured CUDA graph replayable.
 // Every wait is bounded; on expiry the kernel records
 // {code, rank, epoch, phase, peer, seen} in `status` (8 ints) and returns without touching
 // data it could not prove complete.  Data moves with plain vector ld/st only.
@@ -30,6 +33,11 @@ enum CommMode : int {
   COMM_TWO_SHOT_SHARDED = 1,
 };
 
+enum CommOpt : int {
+  COMM_OPT_ADAMW = 0,   // AdamW / Adam on master, m, v
+  COMM_OPT_SGD = 1,     // SGD with momentum: `m` is the velocity (may be null: plain SGD), `v` unused
+};
+
 struct CommAdamArgs {
   const uint64_t* grad_ptrs = nullptr;    // [world] device table: bf16 gradient arenas
   const uint64_t* signal_ptrs = nullptr;  // [world] device table: signal pads
@@ -37,14 +45,26 @@ struct CommAdamArgs {
   int rank = 0, world = 1;
   int64_t elem_offset = 0;                // first arena element of the bucket
   int64_t n = 0;                          // elements in the bucket (multiple of 8 * world)
-  float* master = nullptr;                // local fp32 arenas (full length, indexed like grads)
+  // NVLS (sharded mode only): multicast addresses of the gradient and shadow arenas.  With
+  // grad_mc the slice is read with multimem.ld_reduce, with shadow_mc the update is published
+  // with multimem.st; null = plain peer loads / stores.
+  const void* grad_mc = nullptr;
+  void* shadow_mc = nullptr;
+  float* master = nullptr;                // local fp32 optimizer state
   float* m = nullptr;
   float* v = nullptr;
+  // Index into master / m / v of the first element this rank updates.  -1: the state arrays
+  // are full length and indexed like the gradients; >= 0: they hold only this rank's shards
+  // (memory-sharded optimizer state) and this bucket's shard starts there.
+  int64_t state_base = -1;
+  int opt_kind = COMM_OPT_ADAMW;
+  float momentum = 0.0f;                  // COMM_OPT_SGD
+  int nesterov = 0;
   const int64_t* seg_end = nullptr;       // weight-decay segments in arena coordinates
   const float* seg_wd = nullptr;
   int nseg = 0;
   AdamArgs adam{};                        // grad_scale carries 1/world (and 1/loss-scale)
-  uint32_t epoch = 0;
+  uint32_t epoch = 0;                     // 0: the kernel numbers itself from its signal pad
   int mode = COMM_ONE_SHOT_REPLICATED;
   int max_blocks = 0;                     // 0 = default
   int* status = nullptr;                  // [8] device ints, zero when healthy

@@ -17,10 +17,14 @@ forward's).  Everything else a step needs — tile choices, split-K workspaces, 
 tape's closures — is fixed at capture time, so shapes must stay the same; build a second
 GraphedStep for another batch shape.
 
-Limits: one rank (the fused collectives take their epoch number as a launch argument) and
-parameters in a flat arena (wrap the model in `distributed.DDP`, which at one rank is just the
-arena plus the fused optimizer launch).  The reference has no counterpart; it issues every op
-from LuaJIT (lua/luatorch/autograd.lua:52-93, lua/luatorch/optim/adam.lua:44-86).
+Several ranks: the fused gradient collectives number themselves from a counter in their
+signal pad and read lr / bias corrections from the same device words, so the captured step
+(forward, backward, the per-bucket reduce + optimizer kernels on the side stream) replays on
+every rank; all ranks must call the step the same number of times.
+
+Limit: parameters in a flat arena (wrap the model in `distributed.DDP`, which at one rank is
+just the arena plus the fused optimizer launch).  The reference has no counterpart; it issues
+every op from LuaJIT (lua/luatorch/autograd.lua:52-93, lua/luatorch/optim/adam.lua:44-86).
 """
 from __future__ import annotations
 
@@ -54,10 +58,6 @@ class GraphedStep:
             pdl = os.environ.get("LT_GRAPH_PDL", "0") == "1"
         if not torch.cuda.is_available():
             raise RuntimeError("GraphedStep needs a CUDA device")
-        from .. import distributed as dist_mod
-        if dist_mod.world_size() > 1:
-            raise NotImplementedError("GraphedStep runs on one rank: the fused collectives take "
-                                      "their epoch as a launch argument")
         if getattr(optimizer, "arena", None) is None:
             raise ValueError("GraphedStep needs the optimizer's parameters in a flat arena "
                              "(wrap the model in distributed.DDP before building the optimizer)")
@@ -86,7 +86,11 @@ class GraphedStep:
         if not pdl:
             B.ext().set_pdl(0)
         try:
-            with torch.cuda.graph(self.graph):
+            # with several ranks the process group's watchdog thread polls CUDA events while
+            # this thread captures: thread-local mode keeps its calls out of the capture
+            from .. import distributed as dist_mod
+            mode = "thread_local" if dist_mod.world_size() > 1 else "global"
+            with torch.cuda.graph(self.graph, capture_error_mode=mode):
                 self.output = step_fn()
         finally:
             B._graph_capture = None

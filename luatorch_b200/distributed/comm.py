@@ -27,7 +27,7 @@ from .. import _backend as B
 _state = {"initialized": False, "rank": 0, "world": 1, "local_rank": 0, "own_pg": False,
           "epoch": 0, "status": None}
 
-SIGNAL_PAD_BYTES = 1024   # start slots [0,16), done slots [16,32), ticket 32 (uint32 each)
+SIGNAL_PAD_BYTES = 1024   # uint32 words: start [0,16), done [16,32), ticket 32, own epoch counter 33
 
 
 def available() -> bool:
@@ -90,8 +90,10 @@ def destroy() -> None:
 
 
 def next_epoch() -> int:
-    """Collective sequence number; identical on every rank as long as all ranks issue the
-    same collectives in the same order."""
+    """Host-side collective sequence number; identical on every rank as long as all ranks
+    issue the same collectives in the same order.  Only the all-gather GEMM takes it: the
+    other collectives pass epoch 0 and number themselves from a counter in their signal pad,
+    which lets a captured CUDA graph be replayed."""
     _state["epoch"] += 1
     return _state["epoch"]
 
@@ -124,9 +126,10 @@ class SymmetricBuffer:
                 self.raw = raw
                 bases = [int(p) for p in hdl.buffer_ptrs]
                 self.peer_mapped = True
+                # NVLink multicast address of the same memory (0 when the machine or the
+                # allocation has none): what multimem.ld_reduce / multimem.st address
                 try:
-                    if hdl.has_multicast_support():
-                        self.multicast_ptr = int(hdl.multicast_ptr)
+                    self.multicast_ptr = int(hdl.multicast_ptr or 0)
                 except Exception:
                     self.multicast_ptr = 0
             except Exception as e:  # pragma: no cover - depends on the machine
@@ -193,7 +196,7 @@ def allreduce_mean_(t: torch.Tensor, buf: Optional[SymmetricBuffer] = None) -> t
             if pad:
                 stage[n:].zero_()
             B.ext().peer_allreduce(buf.ptrs, buf.signal_ptrs, rank(), w, 0, n + pad,
-                                   0 if t.dtype == torch.float32 else 1, 1.0 / w, next_epoch(),
+                                   0 if t.dtype == torch.float32 else 1, 1.0 / w, 0,
                                    status_buffer())
             t.copy_(stage[:n].reshape(t.shape))
             return t
@@ -211,7 +214,7 @@ def broadcast_(t: torch.Tensor, root: int = 0, buf: Optional[SymmetricBuffer] = 
         stage = buf.data[:nbytes]
         if rank() == root:
             stage.copy_(t.contiguous().view(torch.uint8).reshape(-1))
-        B.ext().peer_broadcast(buf.ptrs, buf.signal_ptrs, rank(), w, root, 0, nbytes, next_epoch(),
+        B.ext().peer_broadcast(buf.ptrs, buf.signal_ptrs, rank(), w, root, 0, nbytes, 0,
                                status_buffer())
         if rank() != root:
             t.copy_(stage.view(t.dtype).reshape(t.shape))

@@ -16,12 +16,25 @@ per parameter (ddp.lua:48-61).  This one is real:
     rest of backward.  `mode`:
         "sharded"    two-shot: rank r reduces slice r of the bucket, updates slice r of
                      master / m / v and stores the new bf16 weights into every rank's shadow
-                     arena (reduce-scatter + shard AdamW + all-gather in one launch);
+                     arena (reduce-scatter + shard optimizer + all-gather in one launch).
+                     The optimizer state is sharded in MEMORY too: each rank allocates
+                     1/world of master / m / v (`shard_state=False` keeps them full length).
+                     With NVLS (`nvls`, default on where the buffers have a multicast
+                     address) the slice is read with multimem.ld_reduce and published with
+                     multimem.st: the NVSwitch reduces and replicates;
         "replicated" one-shot: every rank reduces the whole bucket and updates its full
                      replica (least latency; meant for small models);
-        "nccl"       baseline: process-group all_reduce per bucket, then the flat AdamW launch.
+        "auto"       "replicated" when the whole model is one small bucket (<= 4 MB of bf16
+                     gradients), else "sharded";
+        "nccl"       baseline: process-group all_reduce per bucket, then the flat optimizer launch.
+    The fused optimizer body is AdamW / Adam or SGD with momentum
+    (lua/luatorch/optim/adamw.lua:51-102, lua/luatorch/optim/sgd.lua:33-56 in the reference).
   * `optimizer.step()` after `sync_gradients()` keeps working: once an optimizer is attached
     its `step` only finalises the fused update (joins the side stream, advances the counter).
+  * checkpoints: `save_checkpoint` / `load_checkpoint` are collectives that assemble the
+    sharded master and moments, so a saved run resumes bit-identically.
+  * one backward per step: the buckets are reduced and applied DURING backward, so a second
+    backward before `zero_grad()` raises; accumulate micro-batches inside `no_sync()`.
 
 Every device-side wait is bounded; `check()` surfaces a timed-out wait as `CommError`.
 """
@@ -33,9 +46,14 @@ import torch
 import torch.distributed as dist
 
 from .. import _backend as B
-from ..parallel.arena import ParamArena
+import contextlib
+import os
+
+from ..parallel.arena import ParamArena, StateShards, bucket_align_for
 from ..tensor import Tensor
 from . import comm
+
+SMALL_MODEL_BYTES = 4 << 20    # "auto": below this one one-shot launch beats the two-shot form
 
 
 class DDP:
@@ -46,14 +64,21 @@ class DDP:
 
     def __init__(self, model, num_gpus: Optional[int] = None, bucket_mb: float = 32.0,
                  mode: str = "sharded", device: Optional[str] = None, max_blocks: int = 0,
-                 broadcast_init: bool = True):
+                 broadcast_init: bool = True, shard_state: bool = True,
+                 nvls: Optional[bool] = None):
         comm.init(num_gpus)
         self.model = model
         self.world = comm.world_size()
         self.rank = comm.rank()
         self.num_gpus = self.world
+        if mode not in ("sharded", "replicated", "nccl", "auto"):
+            raise ValueError("unknown mode %r" % (mode,))
         self.mode = mode
         self.max_blocks = max_blocks
+        self._accumulate = False
+        self.comm_ms: List[float] = []      # per-bucket device time of the last profiled step
+        self._profile = False
+        self._bucket_events = []
         self.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         self.optimizer = None
         self._step_check = 0
@@ -74,7 +99,7 @@ class DDP:
         self.arena = ParamArena(model.parameters(), device=self.device,
                                 compute_dtype=torch.bfloat16 if on_gpu else None,
                                 grad_dtype=torch.bfloat16 if on_gpu else torch.float32,
-                                allocator=allocator)
+                                allocator=allocator, bucket_align=bucket_align_for(self.world))
         if on_gpu:
             self.shadow_buf = self._bufs[0]
             self.grad_buf = self._bufs[1]
@@ -82,10 +107,20 @@ class DDP:
         else:
             self.shadow_buf = self.grad_buf = None
             self.peer = False
+        if self.mode == "auto":
+            self.mode = "replicated" if self.arena.total * 2 <= SMALL_MODEL_BYTES else "sharded"
         if self.world > 1 and self.mode != "nccl" and not self.peer:
             self.mode = "nccl"   # no peer mapping on this machine: process-group collectives
         bucket_elems = max(2048, int(bucket_mb * 1024 * 1024 / 2))
         self.buckets = self.arena.buckets(bucket_elems)
+        # NVLS: multicast addresses of the two arenas (sharded mode only)
+        want_nvls = (os.environ.get("LT_NVLS", "1") != "0") if nvls is None else bool(nvls)
+        self.grad_mc = self.shadow_mc = 0
+        if (want_nvls and on_gpu and self.peer and self.mode == "sharded" and
+                self.grad_buf.multicast_ptr and self.shadow_buf.multicast_ptr):
+            self.grad_mc = self.grad_buf.multicast_ptr + comm.SIGNAL_PAD_BYTES
+            self.shadow_mc = self.shadow_buf.multicast_ptr + comm.SIGNAL_PAD_BYTES
+        self.nvls = bool(self.grad_mc)
         self._unit_bucket = {}
         for bi, b in enumerate(self.buckets):
             for u in b["units"]:
@@ -98,10 +133,18 @@ class DDP:
             u._hook = self._on_grad_ready
         if broadcast_init and self.world > 1:
             self._broadcast_parameters()
+        self._state_base = [-1] * len(self.buckets)
+        if shard_state and on_gpu and self.peer and self.mode == "sharded" and self.world > 1:
+            shards = StateShards(self.buckets, self.rank, self.world)
+            self.arena.shard_state(shards)
+            self._state_base = [off for (_, _, off) in shards.pieces]
+        self._written = set()
         self._reset_step()
         if self.rank == 0:
-            print("DDP: model replicated across %d gpus (%s, %d buckets)" % (
-                self.world, self.mode, len(self.buckets)))
+            print("DDP: model replicated across %d gpus (%s%s%s, %d buckets)" % (
+                self.world, self.mode, ", nvls" if self.nvls else "",
+                ", state sharded" if self.arena.state_shards is not None else "",
+                len(self.buckets)))
 
     # ------------------------------------------------------------------ reference surface
     def forward(self, *args, **kwargs):
@@ -168,8 +211,32 @@ class DDP:
         self._cursor = 0
         self._synced = False
         self._comm_used = False      # did this step put work on the communication stream?
+        self._written.clear()
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this block only accumulate into the gradient arena
+        (`accumulate=True` GEMM epilogues); the first backward after it reduces and applies
+        the sum.  Use it for gradient accumulation over micro-batches."""
+        self._accumulate = True
+        try:
+            yield self
+        finally:
+            self._accumulate = False
+            # the units counted down inside the block are counted again by the next backward
+            for bi, b in enumerate(self.buckets):
+                self._pending[bi] = len(b["units"])
+            self._written.clear()
 
     def _on_grad_ready(self, unit: Tensor) -> None:
+        if self._accumulate:
+            return
+        if id(unit) in self._written:
+            raise RuntimeError(
+                "DDP: a second backward reached parameter gradients that were already reduced "
+                "and applied in this step; call zero_grad() between steps, or run the extra "
+                "backward passes inside `with ddp.no_sync():`")
+        self._written.add(id(unit))
         for bi in self._unit_bucket.get(id(unit), ()):
             self._pending[bi] -= 1
         self._launch_ready()
@@ -177,12 +244,31 @@ class DDP:
     def _launch_ready(self, force: bool = False) -> None:
         # buckets go out strictly in index order so every rank issues the same sequence
         while self._cursor < len(self.buckets) and (force or self._pending[self._cursor] <= 0):
+            if force and self._pending[self._cursor] > 0:
+                self._zero_unwritten(self._cursor)
             self._launch_bucket(self._cursor)
             self._cursor += 1
 
+    def _zero_unwritten(self, bi: int) -> None:
+        """A parameter that took no part in this step's graph has no gradient: its slot still
+        holds an earlier step's values and is cleared before the bucket is reduced."""
+        for u in self.buckets[bi]["units"]:
+            if id(u) not in self._written and u._grad_buf is not None:
+                u._grad_buf.zero_()
+
+    def _opt_kind(self) -> int:
+        """0 AdamW / Adam, 1 SGD, -1 nothing this wrapper can fuse."""
+        opt = self.optimizer
+        if opt is None or self.device != "cuda":
+            return -1
+        if hasattr(opt, "beta1"):
+            return 0
+        if hasattr(opt, "momentum"):
+            return 1
+        return -1
+
     def _fusable(self) -> bool:
-        return (self.optimizer is not None and self.device == "cuda" and
-                hasattr(self.optimizer, "beta1"))
+        return self._opt_kind() >= 0
 
     def _launch_bucket(self, bi: int) -> None:
         if self._launched[bi]:
@@ -204,24 +290,51 @@ class DDP:
         self._comm_stream.wait_event(ev)
         self._comm_used = True
         with torch.cuda.stream(self._comm_stream):
+            if self._profile:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record()
             opt = self.optimizer
-            if self._fusable() and (self.world == 1 or self.mode in ("sharded", "replicated")):
-                t = opt.t + 1
-                bc1, bc2 = 1.0 - opt.beta1 ** t, 1.0 - opt.beta2 ** t
-                seg_end, seg_wd = opt.segments()
+            kind = self._opt_kind()
+            if kind >= 0 and (self.world == 1 or self.mode in ("sharded", "replicated")):
+                cap = B._graph_capture
+                if cap is not None:
+                    cap.uses_optimizer = True
+                if kind == 0:
+                    t = opt.t + 1
+                    bc1, bc2 = 1.0 - opt.beta1 ** t, 1.0 - opt.beta2 ** t
+                    seg_end, seg_wd = opt.segments()
                 if self.world == 1:
-                    B.adamw_flat(a.master[lo:hi], a.shadow[lo:hi], a.grad[lo:hi],
-                                 opt.m_flat[lo:hi], opt.v_flat[lo:hi],
-                                 (seg_end - lo).clamp_(min=0), seg_wd, opt.lr, opt.beta1,
-                                 opt.beta2, opt.epsilon, bc1, bc2, opt.grad_scale,
-                                 opt.skip_flag)
+                    if kind == 0:
+                        B.adamw_flat(a.master[lo:hi], a.shadow[lo:hi], a.grad[lo:hi],
+                                     opt.m_flat[lo:hi], opt.v_flat[lo:hi],
+                                     self._bucket_segments(bi, seg_end), seg_wd, opt.lr, opt.beta1,
+                                     opt.beta2, opt.epsilon, bc1, bc2, opt.grad_scale,
+                                     opt.skip_flag)
+                    else:
+                        B.sgd_flat(a.master[lo:hi], a.shadow[lo:hi], a.grad[lo:hi],
+                                   opt.v_flat[lo:hi] if opt.momentum else None, opt.lr,
+                                   opt.momentum, opt.nesterov, opt.grad_scale)
                 else:
-                    B.ext().allreduce_adamw(
-                        self.grad_buf.ptrs, self.grad_buf.signal_ptrs, self.rank, self.world, lo,
-                        hi - lo, a.master, self.shadow_buf.ptrs, opt.m_flat, opt.v_flat, seg_end,
-                        seg_wd, opt.lr, opt.beta1, opt.beta2, opt.epsilon, bc1, bc2,
-                        opt.grad_scale / self.world, comm.next_epoch(),
-                        1 if self.mode == "sharded" else 0, self.max_blocks, comm.status_buffer())
+                    sharded = self.mode == "sharded"
+                    master = a.master_shard if a.state_shards is not None else a.master
+                    dyn = cap.dyn_opt if cap is not None else None
+                    if kind == 0:
+                        B.ext().allreduce_adamw(
+                            self.grad_buf.ptrs, self.grad_buf.signal_ptrs, self.rank, self.world, lo,
+                            hi - lo, master, self.shadow_buf.ptrs, opt.m_flat, opt.v_flat, seg_end,
+                            seg_wd, opt.lr, opt.beta1, opt.beta2, opt.epsilon, bc1, bc2,
+                            opt.grad_scale / self.world, 0, 1 if sharded else 0, self.max_blocks,
+                            comm.status_buffer(), self._state_base[bi], 0, 0.0, False,
+                            self.grad_mc, self.shadow_mc, opt.skip_flag, dyn)
+                    else:
+                        B.ext().allreduce_adamw(
+                            self.grad_buf.ptrs, self.grad_buf.signal_ptrs, self.rank, self.world, lo,
+                            hi - lo, master, self.shadow_buf.ptrs,
+                            opt.v_flat if opt.momentum else None, None, None, None, opt.lr, 0.0,
+                            0.0, 0.0, 1.0, 1.0, opt.grad_scale / self.world, 0,
+                            1 if sharded else 0, self.max_blocks, comm.status_buffer(),
+                            self._state_base[bi], 1, opt.momentum, opt.nesterov, self.grad_mc,
+                            self.shadow_mc, None, dyn)
             elif self.world > 1:
                 if self.mode == "nccl" or not self.peer:
                     g = a.grad[lo:hi]
@@ -230,11 +343,25 @@ class DDP:
                 else:
                     B.ext().peer_allreduce(self.grad_buf.ptrs, self.grad_buf.signal_ptrs,
                                            self.rank, self.world, lo, hi - lo, 1, 1.0 / self.world,
-                                           comm.next_epoch(), comm.status_buffer())
+                                           0, comm.status_buffer())
+            if self._profile:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                self._bucket_events.append((bi, e0, e1))
+
+    def _bucket_segments(self, bi: int, seg_end: torch.Tensor) -> torch.Tensor:
+        """Weight-decay segment ends in the bucket's own coordinates (built once per bucket)."""
+        cache = getattr(self, "_seg_cache", None)
+        if cache is None or cache[0] is not seg_end:
+            cache = self._seg_cache = (seg_end, {})
+        t = cache[1].get(bi)
+        if t is None:
+            t = cache[1][bi] = (seg_end - self.buckets[bi]["start"]).clamp_(min=0)
+        return t
 
     def sync_gradients(self) -> None:
         """Make sure every bucket has been issued and the compute stream waits for them."""
-        if self._synced:
+        if self._synced or self._accumulate:
             return
         self._launch_ready(force=True)
         # join the communication stream only if this step forked onto it (a stream that did no
@@ -247,13 +374,41 @@ class DDP:
 
     def _optimizer_step(self) -> None:
         opt = self.optimizer
+        if self._accumulate:
+            return
         self.sync_gradients()
         fused = self._fusable() and (self.world == 1 or self.mode in ("sharded", "replicated"))
         if fused:
-            opt.t += 1
+            if hasattr(opt, "t"):
+                opt.t += 1
         else:
             opt._plain_step()
         self._step_check += 1
+
+    # ------------------------------------------------------------------ communication profile
+    def profile_next_step(self, on: bool = True) -> None:
+        """Record CUDA events around every bucket's kernel during the following steps;
+        `comm_profile()` reads them."""
+        self._profile = bool(on)
+        self._bucket_events = []
+
+    def comm_profile(self) -> dict:
+        """Per-bucket device time of the fused collective kernels recorded since
+        `profile_next_step()` (ms), their sum, and how much of it ran under backward:
+        overlap = 1 - (time the compute stream waited at sync_gradients) / (bucket time)
+        is estimated as the share of bucket time that ended before the last bucket started."""
+        if not self._bucket_events:
+            return {"buckets_ms": [], "total_ms": 0.0, "overlap": 0.0}
+        torch.cuda.synchronize()
+        per = {}
+        for bi, e0, e1 in self._bucket_events:
+            per.setdefault(bi, []).append(e0.elapsed_time(e1))
+        ms = [sum(v) / len(v) for _, v in sorted(per.items())]
+        total = sum(ms)
+        exposed = ms[-1] if ms else 0.0     # the last bucket cannot start before backward ends
+        self.comm_ms = ms
+        return {"buckets_ms": ms, "total_ms": total,
+                "overlap": (1.0 - exposed / total) if total > 0 else 0.0}
 
     def check(self) -> None:
         """Surface device-side communication errors (one small device-to-host read)."""
@@ -261,16 +416,56 @@ class DDP:
             comm.check_status()
 
     def gather_master(self) -> None:
-        """In "sharded" mode each rank owns the fp32 master of its bucket slices only; this
-        refreshes the other slices from their owners (before writing a checkpoint)."""
+        """Collective.  In "sharded" mode each rank owns the fp32 master of its bucket slices
+        only; this assembles the full master on every rank (before writing a checkpoint).
+        With memory-sharded state the full copy is temporary: `release_master()` drops it."""
         if self.world == 1 or self.mode != "sharded":
             return
         a = self.arena
+        if a.state_shards is not None:
+            a.materialize_master()
+            return
         for b in self.buckets:
             lo, hi = b["start"], b["end"]
             span = (hi - lo) // self.world
-            parts = [torch.empty(span, device=a.master.device, dtype=torch.float32)
-                     for _ in range(self.world)]
-            dist.all_gather(parts, a.master[lo + self.rank * span: lo + (self.rank + 1) * span].contiguous())
-            for r, p in enumerate(parts):
-                a.master[lo + r * span: lo + (r + 1) * span].copy_(p)
+            dist.all_gather_into_tensor(
+                a.master[lo:lo + span * self.world],
+                a.master[lo + self.rank * span: lo + (self.rank + 1) * span].clone())
+
+    def release_master(self, write_back: bool = False) -> None:
+        self.arena.release_master(write_back)
+
+    def save_checkpoint(self, path: str, optimizer=None, scheduler=None, scaler=None,
+                        step: int = 0, extra: Optional[dict] = None) -> None:
+        """Collective: every rank calls it, rank 0 writes.  `path` receives the parameters in
+        the reference's byte format (lua/luatorch/io/checkpoint.lua:26-56); `path.opt.bin` /
+        `path.state.json` receive the optimizer moments (gathered from their owners when the
+        state is sharded), step, schedule, scaler and RNG state."""
+        from ..io import checkpoint
+        optimizer = optimizer if optimizer is not None else self.optimizer
+        if self.device == "cuda":
+            torch.cuda.synchronize()
+        self.gather_master()
+        sd = optimizer.state_dict() if optimizer is not None else None
+        if self.rank == 0:
+            checkpoint.save(self.model, path)
+            checkpoint.save_training_state(path, self.model, optimizer, scheduler, scaler,
+                                           step=step, extra=extra, optimizer_state=sd)
+        self.release_master()
+        comm.barrier()
+
+    def load_checkpoint(self, path: str, optimizer=None, scheduler=None, scaler=None) -> dict:
+        """Collective counterpart of `save_checkpoint`; returns the saved metadata."""
+        from ..io import checkpoint
+        optimizer = optimizer if optimizer is not None else self.optimizer
+        self.gather_master()
+        checkpoint.load(self.model, path)
+        if self.arena.state_shards is not None:
+            self.release_master(write_back=True)
+        else:
+            self.arena.sync_shadow()
+        meta = checkpoint.load_training_state(path, self.model, optimizer, scheduler, scaler)
+        if self.device == "cuda":
+            torch.cuda.synchronize()
+        comm.barrier()
+        return meta

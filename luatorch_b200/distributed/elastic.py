@@ -103,6 +103,10 @@ def resume(build_fn: Callable[[], tuple], checkpoint_path: str):
     parameters and training state saved by `io.checkpoint.save` / `save_training_state`."""
     from ..io import checkpoint
     model, optimizer, scheduler, scaler = build_fn()
+    if hasattr(model, "load_checkpoint"):
+        # the data-parallel wrapper restores sharded master weights and moments itself
+        meta = model.load_checkpoint(checkpoint_path, optimizer, scheduler, scaler)
+        return model, optimizer, scheduler, scaler, meta
     inner = getattr(model, "model", model)
     checkpoint.load(inner, checkpoint_path)
     arena = getattr(model, "arena", None)

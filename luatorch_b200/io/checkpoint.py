@@ -122,11 +122,14 @@ def _module_buffers(model) -> List[Tensor]:
 
 
 def save_training_state(path: str, model=None, optimizer=None, scheduler=None, scaler=None,
-                        step: int = 0, extra: Optional[dict] = None) -> None:
+                        step: int = 0, extra: Optional[dict] = None,
+                        optimizer_state: Optional[dict] = None) -> None:
+    """`optimizer_state`: a state_dict() taken beforehand (with state sharded over ranks,
+    state_dict() is a collective that every rank has to enter, while only one rank writes)."""
     tensors: List[torch.Tensor] = []
     meta = {"step": int(step), "extra": extra or {}, "format": 1}
     if optimizer is not None:
-        sd = optimizer.state_dict()
+        sd = optimizer_state if optimizer_state is not None else optimizer.state_dict()
         groups = {}
         for k, v in sd.items():
             if isinstance(v, list) and v and isinstance(v[0], torch.Tensor):

@@ -66,10 +66,16 @@ class Adam:
             self.arena = next(iter(arenas.values()))
         if self.arena is not None:
             a = self.arena
-            self.m_flat = torch.zeros(a.total, device=a.device, dtype=torch.float32)
-            self.v_flat = torch.zeros(a.total, device=a.device, dtype=torch.float32)
-            self.m = [self.m_flat[o:o + u.numel()].view(u._t.shape) for u, o in zip(a.units, a.offsets)]
-            self.v = [self.v_flat[o:o + u.numel()].view(u._t.shape) for u, o in zip(a.units, a.offsets)]
+            # with memory-sharded state (distributed.DDP mode "sharded") the moments cover only
+            # this rank's slices of the arena: 1/world of its length
+            n_state = a.state_numel()
+            self.m_flat = torch.zeros(n_state, device=a.device, dtype=torch.float32)
+            self.v_flat = torch.zeros(n_state, device=a.device, dtype=torch.float32)
+            if a.state_shards is None:
+                self.m = [self.m_flat[o:o + u.numel()].view(u._t.shape) for u, o in zip(a.units, a.offsets)]
+                self.v = [self.v_flat[o:o + u.numel()].view(u._t.shape) for u, o in zip(a.units, a.offsets)]
+            else:
+                self.m = self.v = None      # per-tensor views exist only after a gather
             self._segments = None
         else:
             self.m = [torch.zeros_like(u._t, dtype=torch.float32) for u in self.units]
@@ -97,6 +103,9 @@ class Adam:
         bc2 = 1.0 - self.beta2 ** self.t
         if self.arena is not None:
             a = self.arena
+            if a.state_shards is not None:
+                raise RuntimeError("optimizer state is sharded over the ranks: step() runs inside "
+                                   "the fused collective (distributed.DDP.attach(optimizer))")
             seg_end, seg_wd = self.segments()
             if a.master.is_cuda:
                 B.adamw_flat(a.master, a.shadow, a.grad, self.m_flat, self.v_flat, seg_end,
@@ -135,6 +144,10 @@ class Adam:
 
     def reset(self) -> None:
         self.t = 0
+        if self.arena is not None:
+            self.m_flat.zero_()
+            self.v_flat.zero_()
+            return
         for m, v in zip(self.m, self.v):
             m.zero_()
             v.zero_()
@@ -144,12 +157,33 @@ class Adam:
 
     # ------------------------------------------------------------------ (de)serialisation
     def state_dict(self) -> dict:
+        """Moments per storage tensor, on the CPU.  With sharded state this is a COLLECTIVE:
+        every rank calls it and every rank receives the full moments."""
+        a = self.arena
+        if a is not None and a.state_shards is not None:
+            out = {"t": self.t, "lr": self.lr}
+            for key, flat in (("m", self.m_flat), ("v", self.v_flat)):
+                full = a.state_shards.gather(flat, a.total)
+                out[key] = [full[o:o + u.numel()].view(u._grad_buf.shape).cpu()
+                            for u, o in zip(a.units, a.offsets)]
+                del full
+            return out
         return {"t": self.t, "lr": self.lr, "m": [m.detach().cpu().clone() for m in self.m],
                 "v": [v.detach().cpu().clone() for v in self.v]}
 
     def load_state_dict(self, state: dict) -> None:
         self.t = int(state["t"])
         self.lr = float(state["lr"])
+        a = self.arena
+        if a is not None and a.state_shards is not None:
+            # every rank holds the full saved moments and keeps its own slices
+            for key, flat in (("m", self.m_flat), ("v", self.v_flat)):
+                full = torch.zeros(a.total, device=flat.device, dtype=torch.float32)
+                for u, o, src in zip(a.units, a.offsets, state[key]):
+                    full[o:o + u.numel()].copy_(src.reshape(-1))
+                a.state_shards.take(full, out=flat)
+                del full
+            return
         for dst, src in zip(self.m, state["m"]):
             dst.copy_(src.reshape(dst.shape))
         for dst, src in zip(self.v, state["v"]):

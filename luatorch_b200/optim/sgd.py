@@ -35,13 +35,19 @@ class SGD:
             self.arena = next(iter(arenas.values()))
         if self.arena is not None:
             a = self.arena
-            self.v_flat = torch.zeros(a.total, device=a.device, dtype=torch.float32)
-            self.velocity = [self.v_flat[o:o + u.numel()].view(u._t.shape)
-                             for u, o in zip(a.units, a.offsets)]
+            self.v_flat = torch.zeros(a.state_numel(), device=a.device, dtype=torch.float32)
+            if a.state_shards is None:
+                self.velocity = [self.v_flat[o:o + u.numel()].view(u._t.shape)
+                                 for u, o in zip(a.units, a.offsets)]
+            else:
+                self.velocity = None     # sharded over the ranks; see state_dict()
         else:
             self.velocity = [torch.zeros_like(u._t, dtype=torch.float32) for u in self.units]
 
     def step(self) -> None:
+        if self.arena is not None and self.arena.state_shards is not None:
+            raise RuntimeError("optimizer state is sharded over the ranks: step() runs inside "
+                               "the fused collective (distributed.DDP.attach(optimizer))")
         if self.arena is not None and self.arena.master.is_cuda:
             a = self.arena
             B.sgd_flat(a.master, a.shadow, a.grad, self.v_flat if self.momentum else None,
@@ -73,6 +79,9 @@ class SGD:
                 u._compute.copy_(u._t)
 
     def reset(self) -> None:
+        if self.arena is not None:
+            self.v_flat.zero_()
+            return
         for v in self.velocity:
             v.zero_()
 
@@ -80,10 +89,23 @@ class SGD:
         self.lr = lr
 
     def state_dict(self) -> dict:
+        """With sharded state a COLLECTIVE: every rank calls it and receives the full velocity."""
+        a = self.arena
+        if a is not None and a.state_shards is not None:
+            full = a.state_shards.gather(self.v_flat, a.total)
+            return {"lr": self.lr, "velocity": [full[o:o + u.numel()].view(u._grad_buf.shape).cpu()
+                                                for u, o in zip(a.units, a.offsets)]}
         return {"lr": self.lr, "velocity": [v.detach().cpu().clone() for v in self.velocity]}
 
     def load_state_dict(self, state: dict) -> None:
         self.lr = float(state["lr"])
+        a = self.arena
+        if a is not None and a.state_shards is not None:
+            full = torch.zeros(a.total, device=self.v_flat.device, dtype=torch.float32)
+            for u, o, src in zip(a.units, a.offsets, state["velocity"]):
+                full[o:o + u.numel()].copy_(src.reshape(-1))
+            a.state_shards.take(full, out=self.v_flat)
+            return
         for dst, src in zip(self.velocity, state["velocity"]):
             dst.copy_(src.reshape(dst.shape))
 

@@ -23,7 +23,54 @@ from .. import _backend as B
 from ..tensor import Tensor
 
 ALIGN = 256          # elements per storage-unit granule
-BUCKET_ALIGN = 2048  # bucket boundaries (multiple of 8 * 16 ranks * ...) in elements
+BUCKET_ALIGN = 2048  # bucket boundaries in elements: a multiple of 8 * world for worlds 2, 4, 8, 16
+
+
+def bucket_align_for(world: int) -> int:
+    """Bucket boundaries must be multiples of 8 * world (16-byte vectors, one slice per rank):
+    2048 for power-of-two worlds, lcm(2048, 8 * world) otherwise (3, 5, 6, 7 ranks)."""
+    import math
+    w = max(1, int(world))
+    return BUCKET_ALIGN * (8 * w) // math.gcd(BUCKET_ALIGN, 8 * w)
+
+
+class StateShards:
+    """Memory-sharded optimizer state: of every bucket [start, end) rank r keeps slice r, and
+    the slices of all buckets sit back to back in one compact tensor per state array (fp32
+    master, m, v), `numel` = arena size / world elements long.  `pieces[i]` = (start, span,
+    shard_offset) of bucket i.  The reference keeps full state on its one device
+    (lua/luatorch/optim/adamw.lua:19-49)."""
+
+    def __init__(self, buckets, rank: int, world: int):
+        self.rank, self.world = int(rank), int(world)
+        self.pieces = []
+        off = 0
+        for b in buckets:
+            span = (b["end"] - b["start"]) // self.world
+            assert span * self.world == b["end"] - b["start"], "bucket not divisible by the world size"
+            self.pieces.append((b["start"], span, off))
+            off += span
+        self.numel = off
+
+    def take(self, full: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """This rank's slices of a full-length arena tensor, compacted."""
+        if out is None:
+            out = torch.empty(self.numel, device=full.device, dtype=full.dtype)
+        for start, span, off in self.pieces:
+            lo = start + self.rank * span
+            out[off:off + span].copy_(full[lo:lo + span])
+        return out
+
+    def gather(self, shard: torch.Tensor, total: int) -> torch.Tensor:
+        """Full-length tensor assembled from every rank's shard (collective: all ranks call)."""
+        import torch.distributed as dist
+        full = torch.zeros(total, device=shard.device, dtype=shard.dtype)
+        for start, span, off in self.pieces:
+            if span == 0:
+                continue
+            dist.all_gather_into_tensor(full[start:start + span * self.world],
+                                        shard[off:off + span].contiguous())
+        return full
 
 _ARENAS: Dict[int, "ParamArena"] = {}
 
@@ -47,8 +94,12 @@ class ParamArena:
     def __init__(self, params: Sequence[Tensor], device: str = "cuda",
                  compute_dtype: Optional[torch.dtype] = torch.bfloat16,
                  grad_dtype: torch.dtype = torch.bfloat16,
-                 allocator: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None):
+                 allocator: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None,
+                 bucket_align: int = BUCKET_ALIGN):
         self.params = list(params)
+        self.bucket_align = int(bucket_align)
+        self.state_shards: Optional[StateShards] = None
+        self.master_shard: Optional[torch.Tensor] = None
         self.units = storage_units(self.params)
         self.device = torch.device(device)
         self.offsets: List[int] = []
@@ -57,7 +108,7 @@ class ParamArena:
             self.offsets.append(off)
             off += (u.numel() + ALIGN - 1) // ALIGN * ALIGN
         self.used = off
-        self.total = (off + BUCKET_ALIGN - 1) // BUCKET_ALIGN * BUCKET_ALIGN
+        self.total = (off + self.bucket_align - 1) // self.bucket_align * self.bucket_align
         alloc = allocator or (lambda n, dt: torch.zeros(n, device=self.device, dtype=dt))
         self.master = torch.zeros(self.total, device=self.device, dtype=torch.float32)
         self.shadow = alloc(self.total, compute_dtype) if compute_dtype is not None else None
@@ -68,7 +119,6 @@ class ParamArena:
             n = u.numel()
             shape = list(u._t.shape)
             self.master[o:o + n].copy_(u._t.reshape(-1).to(self.device, torch.float32))
-            u._t = self.master[o:o + n].view(shape)
             u._grad_buf = self.grad[o:o + n].view(shape)
             u._compute = self.shadow[o:o + n].view(shape) if self.shadow is not None else None
             u.grad = None
@@ -77,12 +127,55 @@ class ParamArena:
             if p._base is not None:
                 lo, hi = p._base_slice
                 base = p._base
-                p._t = base._t[:, lo:hi]
                 p._grad_buf = base._grad_buf[:, lo:hi]
                 p._compute = base._compute[:, lo:hi] if base._compute is not None else None
                 p.grad = None
             _ARENAS[id(p)] = self
+        self._point_values(self.master)
         self.sync_shadow()
+
+    def _point_values(self, flat: torch.Tensor) -> None:
+        """Make every parameter's value tensor (`_t`) a view of the flat tensor `flat`."""
+        for u, o in zip(self.units, self.offsets):
+            u._t = flat[o:o + u.numel()].view(list(u._grad_buf.shape))
+        for p in self.params:
+            if p._base is not None:
+                lo, hi = p._base_slice
+                p._t = p._base._t[:, lo:hi]
+
+    # ------------------------------------------------------------------ sharded optimizer state
+    def state_numel(self) -> int:
+        """Length of one optimizer-state array on this rank."""
+        return self.state_shards.numel if self.state_shards is not None else self.total
+
+    def shard_state(self, shards: StateShards) -> None:
+        """Keep only this rank's slices of the fp32 master (and let optimizers built afterwards
+        allocate their moments at shard size).  Parameter values then read from the bf16
+        shadow until `materialize_master()` assembles the full fp32 copy again."""
+        assert self.shadow is not None and self.master is not None
+        self.state_shards = shards
+        self.master_shard = shards.take(self.master)
+        self.master = None
+        self._point_values(self.shadow)
+
+    def materialize_master(self) -> None:
+        """Collective.  Assemble the full fp32 master from every rank's shard (before writing a
+        checkpoint or loading one); parameter values are views of it until release_master()."""
+        if self.state_shards is None or self.master is not None:
+            return
+        self.master = self.state_shards.gather(self.master_shard, self.total)
+        self._point_values(self.master)
+
+    def release_master(self, write_back: bool = False) -> None:
+        """Drop the assembled master again; with `write_back` its values first replace this
+        rank's shard and the bf16 shadow (after loading a checkpoint into it)."""
+        if self.state_shards is None or self.master is None:
+            return
+        if write_back:
+            self.state_shards.take(self.master, out=self.master_shard)
+            self.sync_shadow()
+        self.master = None
+        self._point_values(self.shadow)
 
     # ------------------------------------------------------------------ views / bookkeeping
     def unit_range(self, u: Tensor):
@@ -91,7 +184,7 @@ class ParamArena:
 
     def sync_shadow(self) -> None:
         """shadow <- master (after loading a checkpoint or editing master by hand)."""
-        if self.shadow is None:
+        if self.shadow is None or self.master is None:
             return
         if self.master.is_cuda:
             B.ext().cast_into(self.master, self.shadow)
@@ -127,7 +220,7 @@ class ParamArena:
         bounds = [self.total]
         cur_end = self.total
         for i in range(len(self.units) - 1, -1, -1):
-            start = self.offsets[i] // BUCKET_ALIGN * BUCKET_ALIGN
+            start = self.offsets[i] // self.bucket_align * self.bucket_align
             if cur_end - start >= bucket_elems and start < bounds[-1]:
                 bounds.append(start)
                 cur_end = start

@@ -37,3 +37,13 @@ class StepTimer:
             e1.synchronize()
             return self.e0.elapsed_time(e1)
         return (time.perf_counter() - self.t0) * 1e3
+
+
+def max_over_ranks(ms: float) -> float:
+    """A window's device time as the slowest rank saw it (one small all-reduce)."""
+    if dist_mod.world_size() <= 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device="cuda" if torch.cuda.is_available() else "cpu", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())

@@ -10,7 +10,7 @@ import argparse
 import torch
 
 import luatorch_b200 as lf
-from .common import StepTimer, log
+from .common import StepTimer, log, max_over_ranks
 
 
 class ConvNet(lf.nn.Module):
@@ -42,8 +42,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--batch", type=int, default=128)
-    ap.add_argument("--mode", default="sharded", choices=["replicated", "sharded", "nccl"])
-    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph (1 rank)")
+    ap.add_argument("--mode", default="auto", choices=["auto", "replicated", "sharded", "nccl"])
+    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph (every rank replays its own capture)")
     args = ap.parse_args(argv)
     lf.distributed.init()
     rank, world = lf.distributed.rank(), lf.distributed.world_size()
@@ -68,14 +68,14 @@ def main(argv=None):
         opt.step()
         return loss
 
-    if args.graph and cuda and world == 1:
+    if args.graph and cuda:
         one_step = lf.cuda.GraphedStep(one_step, opt, inputs=(x, y))
     timer = StepTimer()
     for step in range(args.steps):
         loss = one_step()
         if rank == 0 and (step + 1) % max(1, args.steps // 5) == 0:
             print("step %5d  loss %.4f" % (step + 1, loss.item()), flush=True)
-    ms = timer.elapsed_ms()
+    ms = max_over_ranks(timer.elapsed_ms())
     ddp.check()
     log("convnet: %d steps, %.3f ms/step, %.0f images/s over %d gpu(s)" % (
         args.steps, ms / args.steps, args.batch * world * args.steps / (ms * 1e-3), world))

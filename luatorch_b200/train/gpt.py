@@ -9,6 +9,11 @@ use_ddp, export_onnx, print_every, sample_every, save_every, temperature, top_k,
 
 Without --text the tokens are synthetic (uniform over the vocabulary).  Throughput is timed on
 the device with CUDA events.
+
+`use_amp` (examples/gpt.lua:113-118,170-174 in the reference) trains through a `GradScaler`:
+the loss is scaled before backward, the averaged gradients are checked for inf / nan on the
+device, and the optimizer launch skips itself on overflow.  The gradient reduction then runs
+unfused (the skip decision needs the reduced gradients), with full-length optimizer state.
 """
 from __future__ import annotations
 
@@ -41,13 +46,17 @@ def main(argv=None):
     ap.add_argument("--out", default="", help="checkpoint path (.bin)")
     ap.add_argument("--bucket-mb", type=float, default=32.0)
     ap.add_argument("--graph", action="store_true",
-                    help="replay the step as a CUDA graph (one rank; two extra warm-up steps)")
+                    help="replay the step as a CUDA graph (two extra warm-up steps)")
+    ap.add_argument("--amp", action="store_true", help="same as use_amp = true in the config")
+    ap.add_argument("--resume", default="", help="checkpoint path (.bin) to resume from")
     args = ap.parse_args(argv)
     cfg = lf.utils.Config({**DEFAULTS, **PRESETS[args.preset]})
     if args.config:
         cfg.load(args.config)
     if args.max_steps:
         cfg.set("max_steps", args.max_steps)
+    if args.amp:
+        cfg.set("use_amp", True)
     lf.distributed.init()
     rank, world = lf.distributed.rank(), lf.distributed.world_size()
     if rank == 0:
@@ -63,10 +72,14 @@ def main(argv=None):
     model = lf.models.GPT(V, cfg.get("embed_dim"), cfg.get("num_heads"), cfg.get("num_layers"),
                           cfg.get("max_seq_len"), cfg.get("dropout"), pos="learned")
     log(model)
-    ddp = lf.distributed.DDP(model, mode=args.mode, bucket_mb=args.bucket_mb, device=dev)
+    use_amp = bool(cfg.get("use_amp")) and cuda
+    ddp = lf.distributed.DDP(model, mode=args.mode, bucket_mb=args.bucket_mb, device=dev,
+                             shard_state=not use_amp)
     opt = lf.optim.AdamW(ddp.parameters(), cfg.get("lr"), 0.9, 0.95, 1e-8, cfg.get("weight_decay"),
                          model.no_decay_params())
-    ddp.attach(opt)
+    scaler = lf.cuda.amp.GradScaler() if use_amp else None
+    if scaler is None:
+        ddp.attach(opt)      # gradient reduction fused with the optimizer update
     sched = lf.optim.WarmupScheduler(opt, cfg.get("warmup_steps"),
                                      lf.optim.CosineAnnealing(opt, max(1, cfg.get("max_steps") - cfg.get("warmup_steps")),
                                                               cfg.get("lr") * 0.1))
@@ -91,17 +104,28 @@ def main(argv=None):
         lf.autograd.zero_graph()
         ddp.zero_grad()
         loss = crit(ddp(x), y)
-        lf.autograd.backward(loss)
-        ddp.sync_gradients()
-        opt.step()
+        if scaler is not None:
+            lf.autograd.backward(scaler.scale_loss(loss))
+            ddp.sync_gradients()          # averaged over the ranks: every rank takes the same decision
+            scaler.step(opt)
+            scaler.update()
+        else:
+            lf.autograd.backward(loss)
+            ddp.sync_gradients()
+            opt.step()
         return loss
 
+    first_step = 1
+    if args.resume:
+        meta = ddp.load_checkpoint(args.resume, opt, sched, scaler)
+        first_step = int(meta.get("step", 0)) + 1
+        log("resumed from %s at step %d" % (args.resume, first_step - 1))
     runner = None
-    if args.graph and cuda and world == 1:
+    if args.graph and cuda and scaler is None:
         runner = lf.cuda.GraphedStep(one_step, opt, inputs=(x0, y0), warmup=2)
     timer = StepTimer()
     window = 0
-    for step in range(1, cfg.get("max_steps") + 1):
+    for step in range(first_step, cfg.get("max_steps") + 1):
         x, y = batch()
         loss = runner(x, y) if runner is not None else one_step(x, y)
         lr = sched.step()
@@ -119,16 +143,10 @@ def main(argv=None):
             out = model.generate(prompt, cfg.get("gen_tokens"), cfg.get("temperature"), cfg.get("top_k"))
             print("sample:", repr(dataset.tokenizer.decode_tensor(out)))
         if args.out and cfg.get("save_every") and step % cfg.get("save_every") == 0:
-            ddp.gather_master()
-            if rank == 0:
-                lf.io.checkpoint.save(model, args.out)
-                lf.io.checkpoint.save_training_state(args.out, model, opt, sched, None, step=step)
+            ddp.save_checkpoint(args.out, opt, sched, scaler, step=step)     # collective
     if args.out:
-        ddp.gather_master()
-        if rank == 0:
-            lf.io.checkpoint.save(model, args.out)
-            lf.io.checkpoint.save_training_state(args.out, model, opt, sched, None, step=cfg.get("max_steps"))
-            print("saved", args.out)
+        ddp.save_checkpoint(args.out, opt, sched, scaler, step=cfg.get("max_steps"))
+        log("saved", args.out)
     if rank == 0 and cfg.get("export_onnx") and args.out:
         lf.export.onnx.export(model, lf.Tensor.wrap(torch.zeros(1, min(S, 16)).to(dev)), args.out + ".onnx")
     if cuda:

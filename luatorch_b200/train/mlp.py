@@ -2,8 +2,8 @@
 synthetic inputs [batch 256, 784] uniform in [0,1], labels uniform in [0,10),
 Linear(784,256)-ReLU-Dropout(0.2)-Linear(256,10), cross entropy, Adam lr 1e-3, bf16 compute
 with fp32 master weights.  With more than one rank the whole model is one small gradient
-bucket, so this exercises the one-shot fused all-reduce + Adam kernel.  On one rank `--graph`
-replays the whole step as a CUDA graph (the step is launch-bound)."""
+bucket, so this exercises the one-shot fused all-reduce + Adam kernel.  `--graph` replays the
+whole step as a CUDA graph on every rank (the step is launch-bound)."""
 from __future__ import annotations
 
 import argparse
@@ -11,15 +11,15 @@ import argparse
 import torch
 
 import luatorch_b200 as lf
-from .common import StepTimer, log
+from .common import StepTimer, log, max_over_ranks
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--batch", type=int, default=256)
-    ap.add_argument("--mode", default="replicated", choices=["replicated", "sharded", "nccl"])
-    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph (1 rank)")
+    ap.add_argument("--mode", default="auto", choices=["auto", "replicated", "sharded", "nccl"])
+    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph (every rank replays its own capture)")
     args = ap.parse_args(argv)
     lf.distributed.init()
     rank, world = lf.distributed.rank(), lf.distributed.world_size()
@@ -46,7 +46,7 @@ def main(argv=None):
         opt.step()
         return loss
 
-    if args.graph and cuda and world == 1:
+    if args.graph and cuda:
         one_step = lf.cuda.GraphedStep(one_step, opt, inputs=(x, y))
     timer = StepTimer()
     for step in range(args.steps):
@@ -54,7 +54,7 @@ def main(argv=None):
         if (step + 1) % logger.print_every == 0 and rank == 0:
             logger.step = step
             logger.log(loss.item(), None, opt.lr)
-    ms = timer.elapsed_ms()
+    ms = max_over_ranks(timer.elapsed_ms())
     ddp.check()
     log("mlp: %d steps, %.3f ms/step, %.0f samples/s over %d gpu(s), final loss %.4f" % (
         args.steps, ms / args.steps, args.batch * world * args.steps / (ms * 1e-3), world, loss.item()))
