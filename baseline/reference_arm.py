@@ -132,9 +132,21 @@ class Replica:
         lab = self.cpu([self.T])
         for i, t in enumerate(seed_tokens[: self.T]):
             lib.tensor_set(lab, i, float(t))
-        lib.tensor_to_cuda(lab)
-        self.labels = lab
+        self.labels_host = lab            # host template; every step uploads a copy of it
+        self.labels = None
+        self.upload_labels()
         self.step_no = 0
+
+    def upload_labels(self):
+        """The step's labels go host -> device through the reference's own calls:
+        tensor_copy (a host copy) + tensor_to_cuda (pool allocation + cudaMemcpy H2D,
+        csrc/cuda/tensor.cu:17-39).  T float labels = 4 T bytes per step."""
+        self.rt.cudaSetDevice(self.dev)
+        if self.labels is not None:
+            self.lib.tensor_free(self.labels)
+        t = self.lib.tensor_copy(self.labels_host)
+        self.lib.tensor_to_cuda(t)
+        self.labels = t
 
     # -------------------------------------------------------------- helpers
     def _reg(self, t):
@@ -300,10 +312,11 @@ class Replica:
 
 
 class _ClockSampler:
-    """SM clocks and throttle reasons of GPU 0 during the timed region (nvidia-smi, 200 ms)."""
+    """SM clocks and throttle reasons of one GPU during the timed region (nvidia-smi, 200 ms)."""
 
-    def __init__(self):
+    def __init__(self, dev=0):
         self.proc = None
+        self.dev = int(dev)
 
     def start(self):
         import subprocess
@@ -311,7 +324,7 @@ class _ClockSampler:
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", "--query-gpu=" + q,
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.dev), "--query-gpu=" + q,
                                           "--format=csv,noheader,nounits", "-lms", "200"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
@@ -350,12 +363,10 @@ def run(args, cfg):
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     if not os.path.exists(LIB_PATH):
         if rank == 0:
             emit({"unavailable": "baseline/_ref/libluatorch.so is not built (CMake build of the reference)"})
-        return
-    if rank != 0:
-        # the reference's NCCL wrapper drives every device from ONE process: other ranks idle
         return
     cfg = dict(cfg)
     if getattr(args, "micro_batch", 0):
@@ -367,131 +378,110 @@ def run(args, cfg):
     lib = _load()
     n_dev = C.c_int(0)
     rt.cudaGetDeviceCount(C.byref(n_dev))
-    n = max(1, min(args.gpus, n_dev.value))
+    # One process per GPU (the launcher starts `world` of them): each drives the unmodified
+    # library on its own device.  The reference's own multi-GPU path (one process, every
+    # device, luatorch_nccl_allreduce per parameter) cannot run: its single cuBLAS handle is
+    # created on device 0 (csrc/cuda/ops/matmul.cu:21-35) and its one memory pool serves all
+    # devices (csrc/cuda/memory_pool.cu:9-21), so a matmul on device 1 returns cuBLAS status
+    # 13.  The ranks therefore exchange NO gradients: the figure is an upper bound on what
+    # the reference could reach with a working exchange.
+    dev = local_rank % max(1, n_dev.value)
+    rt.cudaSetDevice(dev)
     lib.pool_init()
     import random
-    rng = random.Random(1234)
+    rng = random.Random(1234 + rank)
     tokens = [rng.randrange(cfg["vocab"]) for _ in range(cfg["micro_batch"] * cfg["seq"])]
-    # The reference's memory pool is one list for all devices (csrc/cuda/memory_pool.cu:9-21,
-    # 46-68): a block freed on device 0 is handed to the next allocation on device 1, whose
-    # cudaMemset then fails with "invalid argument".  Its own pool_clear() between devices is
-    # the only way to drive several GPUs from its single process, so the harness calls it
-    # whenever it switches device (this serialises the devices, as the reference would).
-    def switch_device():
-        if n > 1:
-            lib.pool_clear()
-
-    if n > 1:
-        # Probe before building n full replicas (minutes of host-side initialisation): one small
-        # matmul on device 0, which creates the reference's single cuBLAS handle there, then the
-        # same on device 1, where that handle returns an error status (no device fault).
-        try:
-            for dev in (0, 1):          # the handle is created by the first matmul, on device 0
-                rt.cudaSetDevice(dev)
-                lib.pool_clear()
-                sh = (C.c_int64 * 2)(64, 64)
-                a = lib.tensor_new(sh, 2, 0, 0)
-                b = lib.tensor_new(sh, 2, 0, 0)
-                lib.tensor_fill(a, 1.0)
-                lib.tensor_fill(b, 1.0)
-                lib.tensor_to_cuda(a)
-                lib.tensor_to_cuda(b)
-                c = lib.tensor_matmul_cuda(a, b)
-                rt.cudaDeviceSynchronize()
-                for t in (a, b, c):
-                    lib.tensor_free(t)
-            rt.cudaSetDevice(0)
-        except RuntimeError as e:
-            emit({"unavailable": "the reference drives all GPUs from one process but keeps ONE cuBLAS "
-                                 "handle, created on device 0 (csrc/cuda/ops/matmul.cu:21-35), and one "
-                                 "memory pool for all devices (csrc/cuda/memory_pool.cu:9-21): a matmul on "
-                                 "device 1 fails (%s), so it cannot run a GPU-resident step on %d GPUs"
-                                 % (str(e)[:80], n)})
-            return
-    reps = []
+    pg = None
+    if world > 1:
+        import torch.distributed as dist   # host-side rendezvous only: barrier + max of the times
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        pg = dist
     try:
-        for d in range(n):
-            switch_device()
-            reps.append(Replica(lib, rt, d, cfg, tokens))
+        rep = Replica(lib, rt, dev, cfg, tokens)
     except RuntimeError as e:
-        emit({"unavailable": "the reference library failed while building the model: %s" % str(e)[:200]})
+        if rank == 0:
+            emit({"unavailable": "the reference library failed while building the model: %s" % str(e)[:200]})
         return
-    if n > 1:
-        rc = lib.luatorch_nccl_init(n)
-        if rc != 0:
-            emit({"unavailable": "luatorch_nccl_init(%d) failed with %d" % (n, rc)})
-            return
 
     def step():
-        for r in reps:
-            switch_device()
-            r.forward_backward()
-        if n > 1:   # one blocking collective per parameter, as ddp.lua:48-61 does
-            lists = [r.grad_list() for r in reps]
-            for j in range(len(lists[0])):
-                ptrs = (C.c_void_p * n)(*[lists[d][j][1].contents.cuda_data for d in range(n)])
-                lib.luatorch_nccl_allreduce(ptrs, lists[0][j][1].contents.numel, n)
-        for r in reps:
-            r.adam(cfg["lr"], cfg["wd"])
-        return [r.read_loss() for r in reps][0]
+        rep.upload_labels()
+        rep.forward_backward()
+        rep.adam(cfg["lr"], cfg["wd"])
+        return rep.read_loss()
 
     def sync():
-        for d in range(n):
-            rt.cudaSetDevice(d)
-            rt.cudaDeviceSynchronize()
+        rt.cudaSetDevice(dev)
+        rt.cudaDeviceSynchronize()
+        if pg is not None:
+            pg.barrier()
 
     try:
-        _timed_part(args, cfg, rt, lib, reps, n, step, sync, emit)
+        _timed_part(args, cfg, rt, lib, rep, dev, rank, world, pg, step, sync, emit)
     except RuntimeError as e:
-        why = str(e)[:160]
-        if n > 1:
-            # measured on 2 B200s: cuBLAS status 13 from tensor_matmul_cuda on device 1
-            why = ("the reference drives all GPUs from one process but keeps ONE cuBLAS handle, "
-                   "created on device 0 (csrc/cuda/ops/matmul.cu:21-35), and one memory pool for "
-                   "all devices (csrc/cuda/memory_pool.cu:9-21): its matmul fails on device 1 "
-                   "(cublas sgemm status 13), so it cannot run a GPU-resident step on %d GPUs; " % n + why)
-        emit({"unavailable": "the reference library failed on this configuration: " + why})
+        if rank == 0:
+            emit({"unavailable": "the reference library failed on this configuration: " + str(e)[:200]})
+    if pg is not None:
+        pg.barrier()
+        pg.destroy_process_group()
     return
 
 
-def _timed_part(args, cfg, rt, lib, reps, n, step, sync, emit):
-    warmup, steps = max(3, args.warmup), args.steps
-    # the reference's step is long; cap the step count so the arm finishes in minutes
-    steps_run = steps
+def _timed_part(args, cfg, rt, lib, rep, dev, rank, world, pg, step, sync, emit):
+    warmup, steps_run = max(3, args.warmup), args.steps
     for _ in range(warmup):
         step()
     sync()
-    sampler = _ClockSampler()
+    sampler = _ClockSampler(dev)
     sampler.start()
     ev0, ev1 = C.c_void_p(), C.c_void_p()
-    rt.cudaSetDevice(0)
+    rt.cudaSetDevice(dev)
     rt.cudaEventCreate(C.byref(ev0))
     rt.cudaEventCreate(C.byref(ev1))
     rt.cudaEventRecord(ev0, None)
     loss = None
     for _ in range(steps_run):
         loss = step()
-    sync()
-    rt.cudaSetDevice(0)
     rt.cudaEventRecord(ev1, None)
     rt.cudaEventSynchronize(ev1)
+    sync()
     ms = C.c_float(0)
     rt.cudaEventElapsedTime(C.byref(ms), ev0, ev1)
     clocks = sampler.stop()
-    tokens_per_step = cfg["micro_batch"] * cfg["seq"] * n
-    value = tokens_per_step * steps_run / (ms.value * 1e-3)
+    ms_max = ms.value
+    if pg is not None:
+        import torch
+        t = torch.tensor([ms.value], dtype=torch.float64)
+        pg.all_reduce(t, op=pg.ReduceOp.MAX)
+        ms_max = float(t.item())
+    if rank != 0:
+        return
+    B, S = cfg["micro_batch"], cfg["seq"]
+    tokens_per_step = B * S * world
+    value = tokens_per_step * steps_run / (ms_max * 1e-3)
+    n_params = sum(int(p.contents.numel) for p in rep.params)
+    note = ("ops without a reference GPU kernel are replaced by cheaper reference ops (upper bound "
+            "on the reference's throughput); compute dtype fp32, the reference's only one")
+    if world > 1:
+        note += ("; upper bound: one process per GPU, NO gradient exchange, because the reference's "
+                 "own exchange cannot run (one cuBLAS handle on device 0, csrc/cuda/ops/matmul.cu:21-35: "
+                 "a matmul on device 1 returns cuBLAS status 13)")
     emit({"metric": "GPT training tokens/sec (device-timed, max over ranks)", "value": value,
-          "unit": "tokens/s", "n_gpus": n, "steps": steps_run, "warmup": warmup,
-          "ms_per_step": ms.value / steps_run, "higher_is_better": True, "scaling": "weak",
-          "vs_baseline": None, "dtype": "fp32 (the reference's only compute dtype)",
-          "data": "synthetic",
-          "config": {"model": "GPT-124M configuration (untied head)", "global_batch": cfg["micro_batch"] * n,
-                     "seq_len": cfg["seq"], "parallelism": "dp%d, one process drives all devices" % n,
-                     "note": "ops without a reference GPU kernel are replaced by cheaper reference ops "
-                             "(upper bound on the reference's throughput)"},
-          "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * n,
-                  "note": "the loss is read back every step; the C ABI has no GPU embedding gather, so "
-                          "token upload is not part of the reference's GPU path"},
+          "unit": "tokens/s", "n_gpus": world, "steps": steps_run, "warmup": warmup,
+          "ms_per_step": ms_max / steps_run, "higher_is_better": True, "scaling": "weak",
+          "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+          "config": bench_config(getattr(args, "config", "gpt124m"), n_params, B, S, world),
+          "note": note,
+          "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms_max / steps_run,
+                  "h2d_bytes_per_step": 4 * B * S, "d2h_bytes_per_step": 4,
+                  "note": "every timed step uploads its labels (tensor_copy + tensor_to_cuda) and "
+                          "reads the loss back, so the device-timed figure is already end to end"},
           "gpu_launches": None, "clocks": clocks, "final_loss": loss})
-    if n > 1:
-        lib.luatorch_nccl_destroy()
+
+
+def bench_config(name, n_params, micro_batch, seq, world):
+    """The `config` block both arms of bench.py print (same keys, same values)."""
+    return {"model": "GPT-%s (untied head)" % name, "global_batch": micro_batch * world,
+            "micro_batch": micro_batch, "seq_len": seq, "parallelism": "dp%d" % world,
+            "optimizer": "AdamW",
+            "l2": "no flush: per-step working set (activations + optimizer state, > 2 GB) is far "
+                  "larger than the 126 MB L2"}

@@ -57,6 +57,7 @@ def run_ours(args):
     import luatorch_b200 as lf
     from luatorch_b200 import _C  # noqa: F401  (fail loudly without the native extension)
     from luatorch_b200.utils.timing import ClockSampler
+    from baseline.reference_arm import bench_config
 
     cfg = dict(CONFIGS[args.config])
     if args.micro_batch:
@@ -131,7 +132,7 @@ def run_ours(args):
     for i in range(warmup):
         step_resident(i)
     ddp.check()
-    sampler = ClockSampler(dev, 0.1).start()
+    sampler = ClockSampler(dev, 0.025).start()
     ms_dev, launches, last_loss = timed(step_resident, args.steps)
     for i in range(2):
         step_e2e(i)
@@ -149,11 +150,11 @@ def run_ours(args):
             "warmup": warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "GPT-%s (%d params, untied head)" % (args.config, model.num_params()),
-                       "global_batch": B * world, "micro_batch": B, "seq_len": S,
-                       "parallelism": "dp%d" % world, "dp_mode": ddp.mode, "optimizer": "AdamW",
-                       "l2": "no flush: per-step working set (activations + optimizer state, > 2 GB) "
-                             "is far larger than the 126 MB L2"},
+            # the same keys and values as the reference arm prints (baseline/reference_arm.py)
+            "config": bench_config(args.config, model.num_params(), B, S, world),
+            "engine": {"params": model.num_params(), "dp_mode": ddp.mode, "nvls": bool(ddp.nvls),
+                       "state_sharded": ddp.arena.state_shards is not None,
+                       "buckets": len(ddp.buckets)},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 4, "d2h_bytes_per_step": 4,
                     "final_loss": loss_val},

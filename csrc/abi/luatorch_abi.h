@@ -63,6 +63,11 @@ void pool_free(void* ptr);
 void pool_clear(void);
 size_t pool_allocated_bytes(void);
 size_t pool_cached_bytes(void);
+/* extensions: stream-ordered release, debug canaries (memory_pool.cpp) */
+void pool_free_async(void* ptr, void* stream);
+void pool_set_debug(int on);
+int pool_check_canaries(void);
+size_t pool_overruns_seen(void);
 size_t cuda_memory_allocated(void);
 size_t cuda_memory_cached(void);
 

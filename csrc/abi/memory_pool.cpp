@@ -11,13 +11,22 @@
 //     larger requests rounded to 2 MiB and served best-fit from an ordered map (a block at
 //     most 2x the request is accepted, as in the reference);
 //   * stream-ordered reuse: a block released with pool_free_async(ptr, stream) carries an
-//     event and is not handed out again until that event has completed.
+//     event and is not handed out again until that event has completed.  pool_free(ptr)
+//     (no stream) makes the block reusable at once, which is correct for this library's own
+//     tensor_*_cuda ops because they all run on the legacy default stream: the next user's
+//     kernels are ordered after the last user's.  Work on other streams must use
+//     pool_free_async.
+//   * debug mode (pool_set_debug(1), or LT_POOL_DEBUG=1 in the environment): every block
+//     gets a 256-byte canary after the requested bytes, filled with 0xA5; pool_free checks
+//     it and pool_check_canaries() checks every live block, reporting writes past the end
+//     of an allocation on stderr.  This stands in for a memory sanitizer where none can run.
 #include "luatorch_abi.h"
 
 #include <cuda_runtime.h>
 #include <map>
 #include <mutex>
 #include <stdio.h>
+#include <stdlib.h>
 #include <unordered_map>
 #include <vector>
 
@@ -28,7 +37,36 @@ struct Block {
   size_t size;
   int device;
   cudaEvent_t ready;   // nullptr when reusable at once
+  size_t user = 0;     // requested bytes (debug mode: the canary starts here)
 };
+
+constexpr size_t kCanaryBytes = 256;
+constexpr unsigned char kCanaryByte = 0xA5;
+int g_debug = -1;       // -1: read LT_POOL_DEBUG on first use
+size_t g_overruns = 0;  // canaries found damaged so far
+
+bool debug_on() {
+  if (g_debug < 0) {
+    const char* e = getenv("LT_POOL_DEBUG");
+    g_debug = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_debug == 1;
+}
+
+// Returns true when the canary behind `b` is intact (device-to-host copy of 256 bytes).
+bool canary_intact(const Block& b) {
+  unsigned char host[kCanaryBytes];
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (cur != b.device) cudaSetDevice(b.device);
+  const cudaError_t e = cudaMemcpy(host, static_cast<const char*>(b.ptr) + b.user, kCanaryBytes,
+                                   cudaMemcpyDeviceToHost);
+  if (cur != b.device) cudaSetDevice(cur);
+  if (e != cudaSuccess) return false;
+  for (size_t i = 0; i < kCanaryBytes; ++i)
+    if (host[i] != kCanaryByte) return false;
+  return true;
+}
 
 constexpr size_t kMinBlock = 512;
 constexpr size_t kSmallMax = 1 << 20;
@@ -89,16 +127,22 @@ void pool_init(void) {
 }
 
 void* pool_alloc(size_t bytes) {
-  const size_t size = round_up(bytes);
+  std::lock_guard<std::mutex> lock(g_mu);
+  const bool dbg = debug_on();
+  const size_t size = round_up(bytes + (dbg ? kCanaryBytes : 0));
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  std::lock_guard<std::mutex> lock(g_mu);
+  auto arm = [&](Block& b) {   // debug mode: lay the canary behind the user's bytes
+    b.user = bytes;
+    if (dbg) cudaMemset(static_cast<char*>(b.ptr) + bytes, kCanaryByte, kCanaryBytes);
+  };
   DevicePool& p = g_pools[dev];
   for (auto it = p.free_blocks.lower_bound(size); it != p.free_blocks.end() && it->first <= 2 * size; ++it) {
     if (!block_ready(it->second)) continue;
     Block b = it->second;
     p.free_blocks.erase(it);
     g_cached -= b.size;
+    arm(b);
     g_live[b.ptr] = b;
     return b.ptr;
   }
@@ -115,7 +159,9 @@ void* pool_alloc(size_t bytes) {
     }
   }
   g_allocated += size;
-  g_live[ptr] = Block{ptr, size, dev, nullptr};
+  Block nb{ptr, size, dev, nullptr};
+  arm(nb);
+  g_live[ptr] = nb;
   return ptr;
 }
 
@@ -130,6 +176,11 @@ void pool_free_async(void* ptr, void* stream) {
   }
   Block b = it->second;
   g_live.erase(it);
+  if (debug_on() && !canary_intact(b)) {
+    ++g_overruns;
+    fprintf(stderr, "luatorch error: pool: write past the end of a %zu-byte block at %p (device %d)\n",
+            b.user, b.ptr, b.device);
+  }
   if (stream != nullptr) {
     int cur = 0;
     cudaGetDevice(&cur);
@@ -156,6 +207,31 @@ void pool_clear(void) {
     release_cached_locked(d);
   }
   cudaSetDevice(cur);
+}
+
+// Extensions (debug mode, see the top of the file).
+void pool_set_debug(int on) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  g_debug = on ? 1 : 0;
+}
+// Checks the canary of every live block; returns how many are damaged (0 when debug is off).
+int pool_check_canaries(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!debug_on()) return 0;
+  int bad = 0;
+  for (auto& kv : g_live) {
+    if (!canary_intact(kv.second)) {
+      ++bad;
+      fprintf(stderr, "luatorch error: pool: write past the end of a %zu-byte block at %p (device %d)\n",
+              kv.second.user, kv.second.ptr, kv.second.device);
+    }
+  }
+  return bad;
+}
+// Damaged canaries seen so far by pool_free / pool_free_async.
+size_t pool_overruns_seen(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  return g_overruns;
 }
 
 size_t pool_allocated_bytes(void) {

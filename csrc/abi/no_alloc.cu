@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <mutex>
 
 #include "../kernels/ops.h"
 
@@ -15,6 +16,7 @@ constexpr int kMaxDevices = 64;
 // In host code `g_noalloc_scratch` is only a handle for the runtime, not a device pointer;
 // the real address is looked up once per device and cached here.
 float* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;   // two host threads may make a device's first call together
 
 int scratch_for_current_device(float** out) {
   int dev = 0;
@@ -24,6 +26,7 @@ int scratch_for_current_device(float** out) {
             cudaGetErrorString(e));
     return LT_NOALLOC_CUDA_ERROR;
   }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (g_scratch_addr[dev] == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
@@ -50,8 +53,15 @@ extern "C" int lt_column_sum_f32_noalloc(const float* in, int64_t rows, int64_t 
     fprintf(stderr, "luatorch error: no_alloc column sum: bad argument\n");
     return LT_NOALLOC_BAD_ARGUMENT;
   }
+  if (rows == 0) {
+    // the sum over no rows is zero; nothing touches the scratch (cudaMemsetAsync allocates nothing)
+    const cudaError_t e = cudaMemsetAsync(out, 0, sizeof(float) * (size_t)cols,
+                                          static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LT_NOALLOC_OK : LT_NOALLOC_CUDA_ERROR;
+  }
   const int64_t need = lt::column_sum_scratch_floats(rows, cols);
-  if (need > LT_NOALLOC_MAX_SCRATCH_FLOATS) {
+  // 65535 is the largest grid.y: the two-stage path launches one block row per 128 input rows
+  if (need > LT_NOALLOC_MAX_SCRATCH_FLOATS || (rows + 127) / 128 > 65535) {
     fprintf(stderr,
             "luatorch error: no_alloc column sum: [%lld x %lld] needs %lld scratch floats, the "
             "built-in scratch holds %d; use the allocating entry point\n",

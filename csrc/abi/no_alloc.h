@@ -20,10 +20,18 @@
 //     with LT_NOALLOC_TOO_LARGE and a message on stderr, nothing is launched.
 //   * The first call on a device looks up the device address of the scratch array (with that
 //     device current).  Make that first call outside any stream capture.
+//     The same answer is given for more than 65535 slabs of 128 rows (the launch grid's
+//     limit).  rows == 0 writes zeros and uses no scratch.
 //   * All calls share the one array: two calls whose kernels can overlap on the GPU
-//     (different streams, no dependency between them) race on it.  Order them on one stream
-//     or with events.  The array keeps whatever the last call left in it; the kernels write
-//     every scratch element they later read, so no clearing is needed between calls.
+//     (different streams, no dependency between them) race on it.  They also share, with
+//     EVERY other column sum of this library (the regular entry points and the bias-gradient
+//     sums inside a training step included), the per-column-group ticket words that elect
+//     the block which adds up the partial sums: a call that overlaps any other column sum on
+//     another stream can corrupt both results.  Order them on one stream or with events.
+//     The array keeps whatever the last call left in it; the kernels write every scratch
+//     element they later read, so no clearing is needed between calls.
+//   * The first call on a device is safe from several host threads at once (a mutex guards
+//     the address lookup).
 #pragma once
 #include <stdint.h>
 

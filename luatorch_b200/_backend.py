@@ -629,6 +629,18 @@ def attention(q, k, v, causal: bool, scale: Optional[float] = None):
         q4, k4, v4 = (t.to(torch.bfloat16).contiguous().unsqueeze(2) for t in (q, k, v))  # [BH,S,1,D]
         o, lse = ext().flash_forward(q4, k4, v4, causal, scale)
         return o.squeeze(2).to(dt), lse.squeeze(1)
+    if q.is_cuda and D % 8 == 0 and q.shape[1] % 8 == 0:
+        # other head dims: scores, softmax and P V as batched tcgen05 GEMMs + the score-softmax
+        # kernel (no library GEMM on the GPU); the log-sum-exp comes from the row maxima of P
+        dt = q.dtype
+        q4, k4, v4 = (t.to(torch.bfloat16).contiguous().unsqueeze(2) for t in (q, k, v))
+        o, p = _attn_composed_forward(q4, k4, v4, causal, scale)
+        # p holds softmax(s), so lse_i = s_ij - log p_ij for any key j: take each row's
+        # largest probability (never rounded to zero) and recompute that one score in fp32
+        pm, jm = p[:, 0].float().max(-1)                                   # [BH, S]
+        kj = torch.gather(k4[:, :, 0].float(), 1, jm.unsqueeze(-1).expand(-1, -1, D))
+        lse = (q4[:, :, 0].float() * kj).sum(-1) * scale - torch.log(pm)
+        return o.squeeze(2).to(dt), lse
     qf, kf, vf = q.float(), k.float(), v.float()
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if causal:

@@ -44,11 +44,15 @@ def test_gpt_matches_cpu_reference(embed, heads):
     ag.backward(loss)
     assert abs(loss.item() - loss_ref.item()) < 0.05, (loss.item(), loss_ref.item())
     g_gpu = _grads(gpu)
-    worst = 0.0
+    # bf16 activations against the fp32 CPU model: matrices within 3 %; vectors (biases, LN
+    # gains: sums of a few hundred bf16-rounded terms each, small norms) get a looser bound
+    bad = []
     for p, a, b in zip(gpu.parameters(), g_gpu, g_ref):
         r = _rel(a, b)
-        worst = max(worst, r)
-        assert r < 0.12, ("gradient mismatch", p.shape, r)
+        bound = 0.03 if len(p.shape) >= 2 else 0.08
+        if not r < bound:
+            bad.append((tuple(p.shape), round(r, 4), bound))
+    assert not bad, ("gradient mismatch", bad)
     from luatorch_b200 import _C
     assert _C.gemm_device_error() == 0 and _C.attention_device_error() == 0
 
@@ -107,15 +111,6 @@ def test_conv_net_config():
     g = torch.Generator().manual_seed(8)
     x = T.wrap(torch.randn(Bn * 3 * 32 * 32, generator=g).cuda())
     y = T.wrap(torch.randint(0, 10, (Bn,), generator=g).float().cuda())
-
-    def forward(inp):
-        h, oh, ow = c1(inp, Bn, 32, 32, act="relu")
-        h = nn.to_nchw(h, Bn, 32, oh * ow)
-        h, oh, ow = c2(h, Bn, oh, ow, act="relu")
-        h = nn.to_nchw(h, Bn, 64, oh * ow)
-        h, oh, ow = c3(h, Bn, oh, ow, act="relu")
-        h = nn.to_nchw(h, Bn, 128, oh * ow)
-        return fc(T.wrap(h._t.reshape(Bn, 8192)) if False else h.reshape([Bn, 8192]))
 
     # reshape must stay on the tape: use an identity-recorded view
     def flat(h):

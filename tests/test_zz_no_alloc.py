@@ -60,5 +60,12 @@ def test_no_alloc_column_sum_rejects_oversized_and_bad_arguments():
     assert lib.lt_column_sum_noalloc_scratch_floats(rows, cols) > (1 << 20)
     dummy = torch.zeros(8, device="cuda")
     assert lib.lt_column_sum_f32_noalloc(dummy.data_ptr(), rows, cols, cols, dummy.data_ptr(), None) == 2
+    # more 128-row slabs than a launch grid can hold: refused as too large, not a launch error
+    assert lib.lt_column_sum_f32_noalloc(dummy.data_ptr(), 128 * 65536, 1, 1, dummy.data_ptr(), None) == 2
+    # no rows: zeros, whatever the column count, and no scratch is touched
+    out = torch.full((3000,), 5.0, device="cuda")
+    assert lib.lt_column_sum_f32_noalloc(dummy.data_ptr(), 0, 3000, 3000, out.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert torch.all(out == 0)
     assert lib.lt_column_sum_f32_noalloc(None, 4, 2, 2, dummy.data_ptr(), None) == 1
     assert lib.lt_column_sum_f32_noalloc(dummy.data_ptr(), 4, 2, 1, dummy.data_ptr(), None) == 1
