@@ -70,30 +70,61 @@ __global__ void hist_kernel(const void* __restrict__ ids, int id_kind, int64_t n
   if (id >= 0 && id < vocab) atomicAdd(&counts[id], 1);
 }
 
-// Single-CTA exclusive scan (1024 threads, contiguous chunk per thread).
-__global__ void __launch_bounds__(1024)
+// Exclusive scan of the bucket counts with independent CTAs: CTA k owns elements
+// [1024 k, 1024 k + 1024); it first adds up everything before its tile (coalesced reads of at
+// most 4 bytes x vocab from L2, all CTAs in parallel), then scans its own tile.  No CTA waits
+// for another one, and the whole scan is one short launch instead of a serial single-CTA walk.
+constexpr int SCAN_TILE = 1024;
+__global__ void __launch_bounds__(SCAN_TILE)
 scan_kernel(const int* __restrict__ counts, int64_t vocab, int* __restrict__ offsets,
             int* __restrict__ cursor) {
-  __shared__ int sh[1024];
-  const int64_t per = (vocab + 1023) / 1024;
-  const int64_t b = threadIdx.x * per, e = b + per < vocab ? b + per : vocab;
-  int local = 0;
-  for (int64_t i = b; i < e; ++i) local += counts[i];
-  sh[threadIdx.x] = local;
+  __shared__ int sh_warp[32];
+  __shared__ int sh_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t tile0 = (int64_t)blockIdx.x * SCAN_TILE;
+  // ---- sum of all counts before this tile
+  int before = 0;
+  for (int64_t i = threadIdx.x; i < tile0; i += SCAN_TILE) before += counts[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  if (lane == 0) sh_warp[warp] = before;
   __syncthreads();
-  for (int o = 1; o < 1024; o <<= 1) {
-    int v = threadIdx.x >= o ? sh[threadIdx.x - o] : 0;
-    __syncthreads();
-    sh[threadIdx.x] += v;
-    __syncthreads();
+  if (warp == 0) {
+    int t = sh_warp[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) sh_base = t;
   }
-  int run = sh[threadIdx.x] - local;  // exclusive prefix of this chunk
-  for (int64_t i = b; i < e; ++i) {
-    offsets[i] = run;
-    cursor[i] = run;
-    run += counts[i];
+  __syncthreads();
+  const int base = sh_base;
+  // ---- inclusive scan of the tile: warp shuffles, then the warp totals
+  const int64_t idx = tile0 + threadIdx.x;
+  const int mine = idx < vocab ? counts[idx] : 0;
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
   }
-  if (threadIdx.x == 1023) offsets[vocab] = sh[1023];
+  __syncthreads();                       // sh_warp is reused
+  if (lane == 31) sh_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int t = sh_warp[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) t += u;
+    }
+    sh_warp[lane] = t;                   // inclusive totals of warps 0..lane
+  }
+  __syncthreads();
+  const int excl = base + (warp > 0 ? sh_warp[warp - 1] : 0) + incl - mine;
+  if (idx < vocab) {
+    offsets[idx] = excl;
+    cursor[idx] = excl;
+  }
+  if (idx == vocab - 1) offsets[vocab] = excl + mine;
 }
 
 __global__ void fill_kernel(const void* __restrict__ ids, int id_kind, int64_t n, int64_t vocab,
@@ -104,11 +135,47 @@ __global__ void fill_kernel(const void* __restrict__ ids, int id_kind, int64_t n
   if (id >= 0 && id < vocab) pos[atomicAdd(&cursor[id], 1)] = (int)t;
 }
 
+template <typename TG, int V>
+__device__ __forceinline__ void store_grad_vec(TG* p, const float (&f)[V]) {
+  if constexpr (sizeof(TG) == 4) {
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q)
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + 4 * q) =
+          make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+  } else if constexpr (V == 8) {
+    VecIO<TG>::store(p, f);      // one 16-byte store
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) VecIO<TG>::st(p + j, f[j]);
+  }
+}
+template <typename TG, int V>
+__device__ __forceinline__ void load_grad_vec(const TG* p, float (&f)[V]) {
+  if constexpr (sizeof(TG) == 4) {
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + 4 * q);
+      f[4 * q] = t.x; f[4 * q + 1] = t.y; f[4 * q + 2] = t.z; f[4 * q + 3] = t.w;
+    }
+  } else if constexpr (V == 8) {
+    VecIO<TG>::load(p, f);
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) f[j] = VecIO<TG>::ld(p + j);
+  }
+}
+
+// One warp per vocabulary row.  `vec`: dim is a multiple of the 16-byte vector of T and every
+// base pointer is 16-byte aligned, so rows are read and written as 16-byte vectors (the
+// table gradient is mostly rows of zeros: writing them at full width is what this kernel's
+// time consists of).
 template <typename T, typename TG>
 __global__ void __launch_bounds__(256)
 embedding_bwd_sum_kernel(const T* __restrict__ dy, const int* __restrict__ offsets,
                          const int* __restrict__ pos, int* __restrict__ pos_sorted,
-                         TG* __restrict__ dtable, int accumulate, int64_t dim, int64_t vocab) {
+                         TG* __restrict__ dtable, int accumulate, int64_t dim, int64_t vocab,
+                         int vec) {
+  constexpr int V = VecIO<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t v = blockIdx.x * 8ll + (threadIdx.x >> 5);
   if (v >= vocab) return;
@@ -122,6 +189,27 @@ embedding_bwd_sum_kernel(const T* __restrict__ dy, const int* __restrict__ offse
   }
   __syncwarp();
   TG* drow = dtable + v * dim;
+  if (vec) {
+    for (int64_t c0 = (int64_t)lane * V; c0 < dim; c0 += 32 * V) {
+      float acc[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+      for (int i = 0; i < cnt; ++i) {
+        float t[V];
+        VecIO<T>::load(dy + (int64_t)pos_sorted[b + i] * dim + c0, t);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += t[j];
+      }
+      if (accumulate) {
+        float old[V];
+        load_grad_vec<TG, V>(drow + c0, old);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += old[j];
+      }
+      store_grad_vec<TG, V>(drow + c0, acc);
+    }
+    return;
+  }
   for (int64_t c0 = lane; c0 < dim; c0 += 32) {
     float acc = 0.0f;
     for (int i = 0; i < cnt; ++i) acc += VecIO<T>::ld(dy + (int64_t)pos_sorted[b + i] * dim + c0);
@@ -187,7 +275,8 @@ cudaError_t embedding_backward(int dtype, const void* dy, const void* ids, int i
                                                                    ws.counts);
     LT_COUNT_LAUNCH();
   }
-  scan_kernel<<<1, 1024, 0, s>>>(ws.counts, vocab, ws.offsets, ws.cursor);
+  scan_kernel<<<(unsigned)((vocab + SCAN_TILE - 1) / SCAN_TILE), SCAN_TILE, 0, s>>>(
+      ws.counts, vocab, ws.offsets, ws.cursor);
   LT_COUNT_LAUNCH();
   if (n_tokens > 0) {
     fill_kernel<<<(unsigned)((n_tokens + 255) / 256), 256, 0, s>>>(ids, id_kind, n_tokens, vocab,
@@ -196,8 +285,10 @@ cudaError_t embedding_backward(int dtype, const void* dy, const void* ids, int i
   }
   LT_DISPATCH_DTYPE(dtype, T, {
     LT_DISPATCH_DTYPE(grad_dtype, TG, {
+      const int vec = dim % VecIO<T>::N == 0 && is_aligned16(dy) && is_aligned16(dtable) &&
+                      (dim * sizeof(TG)) % 16 == 0;
       embedding_bwd_sum_kernel<T, TG><<<(unsigned)((vocab + 7) / 8), 256, 0, s>>>(
-          (const T*)dy, ws.offsets, ws.pos, ws.pos_sorted, (TG*)dtable, accumulate, dim, vocab);
+          (const T*)dy, ws.offsets, ws.pos, ws.pos_sorted, (TG*)dtable, accumulate, dim, vocab, vec);
       LT_COUNT_LAUNCH();
     })
   })

@@ -5,9 +5,14 @@
 // reference kernel reads each row three times from global memory and has no backward at
 // all (csrc/cuda/ops/fused.cu:63-127); its Lua LayerNorm backward walks elements on the
 // CPU (lua/luatorch/nn/layernorm.lua:76-126).
-// Backward: one warp per row computes dx (optionally adding an incoming residual gradient)
-// while accumulating dgamma / dbeta partials in registers; partials are folded per block in
-// shared memory, written to scratch, and a second kernel reduces them in a fixed order.
+// Backward: ONE kernel.  Each warp walks rows (x and dy of a row stay in registers between the
+// two passes), writes dx (optionally adding an incoming residual gradient) and accumulates
+// its dgamma / dbeta terms in registers; a CTA folds its warps in warp order through shared
+// memory and writes one partial row to scratch; the last CTA of each group of 16 (a ticket
+// counter) adds the group's partials in CTA order, and the last group to finish adds the
+// group sums in group order and writes dgamma / dbeta.  Every sum has a fixed order, so the
+// result does not depend on timing.  (Rows that the vector path cannot address fall back to
+// separate dx / partial / reduce kernels.)
 #include "ops.h"
 #include "common.cuh"
 
@@ -22,13 +27,31 @@ template <typename TP> __device__ __forceinline__ float ldp(const TP* p, int64_t
   return VecIO<TP>::ld(p + i);
 }
 
+// V consecutive parameters starting at element i (i a multiple of V, base 16-byte aligned)
+template <typename TP, int V>
+__device__ __forceinline__ void load_params(const TP* __restrict__ p, int64_t i, float (&f)[V]) {
+  if constexpr (sizeof(TP) == 4) {
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      const float4 t = *reinterpret_cast<const float4*>(p + i + 4 * q);
+      f[4 * q] = t.x; f[4 * q + 1] = t.y; f[4 * q + 2] = t.z; f[4 * q + 3] = t.w;
+    }
+  } else if constexpr (V == 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p + i);
+    VecIO<TP>::unpack(u, f);
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) f[j] = VecIO<TP>::ld(p + i + j);
+  }
+}
+
 // ----------------------------------------------------------------------------- forward
 // NV = 16-byte vectors per lane (row length <= 32 * NV * V elements).
 template <typename T, typename TP, int NV>
 __global__ void __launch_bounds__(THREADS)
 ln_fwd_kernel(const T* __restrict__ x, const TP* __restrict__ gamma, const TP* __restrict__ beta,
               float eps, T* __restrict__ y, float* __restrict__ mean_out,
-              float* __restrict__ rstd_out, int64_t rows, int64_t cols) {
+              float* __restrict__ rstd_out, int64_t rows, int64_t cols, int vec_params) {
   pdl_enter();
   constexpr int V = VecIO<T>::N;
   const int lane = threadIdx.x & 31;
@@ -66,10 +89,16 @@ ln_fwd_kernel(const T* __restrict__ x, const TP* __restrict__ gamma, const TP* _
   for (int i = 0; i < NV; ++i) {
     const int64_t vi = lane + 32 * i;
     if (vi < nvec) {
-      float o[V];
+      float o[V], ga[V], be[V];
+      if (vec_params) {
+        load_params<TP, V>(gamma, vi * V, ga);
+        load_params<TP, V>(beta, vi * V, be);
+      } else {
 #pragma unroll
-      for (int j = 0; j < V; ++j)
-        o[j] = (v[i][j] - mean) * rstd * ldp(gamma, vi * V + j) + ldp(beta, vi * V + j);
+        for (int j = 0; j < V; ++j) { ga[j] = ldp(gamma, vi * V + j); be[j] = ldp(beta, vi * V + j); }
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = (v[i][j] - mean) * rstd * ga[j] + be[j];
       VecIO<T>::store(yr + vi * V, o);
     }
   }
@@ -222,6 +251,161 @@ ln_stats_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* 
   }
 }
 
+// Ticket words of the fused backward: [0] groups finished, [1 + g] CTAs of group g finished.
+// They return to zero at the end of every launch.  Launches that can overlap on the GPU
+// (different streams with no dependency) would share them: keep LayerNorm backward calls
+// ordered on one stream.
+constexpr int FB_GROUP = 16;
+constexpr int FB_MAX_GROUPS = (BWD_MAX_BLOCKS + FB_GROUP - 1) / FB_GROUP;
+__device__ unsigned g_ln_tickets[1 + FB_MAX_GROUPS];
+
+__device__ __forceinline__ void store_grad(void* base, int dtype, int64_t i, float v, int accumulate) {
+  if (dtype == DT_F32) {
+    float* p = static_cast<float*>(base) + i;
+    *p = accumulate ? *p + v : v;
+  } else if (dtype == DT_BF16) {
+    __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base) + i;
+    *p = __float2bfloat16(accumulate ? __bfloat162float(*p) + v : v);
+  } else {
+    __half* p = static_cast<__half*>(base) + i;
+    *p = __float2half(accumulate ? __half2float(*p) + v : v);
+  }
+}
+
+template <typename T, typename TP, int NV>
+__global__ void __launch_bounds__(THREADS, 2)
+ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
+                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                    const T* __restrict__ dx_add, T* __restrict__ dx, int64_t rows, int64_t cols,
+                    float* __restrict__ scratch, void* dgamma, void* dbeta, int grad_dtype,
+                    int accumulate) {
+  pdl_enter();
+  constexpr int V = VecIO<T>::N;
+  extern __shared__ float sh_fold[];       // [2][cols]
+  __shared__ int sh_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t nvec = cols / V;
+  float dg[NV][V], db[NV][V];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) { dg[i][j] = 0.0f; db[i][j] = 0.0f; }
+
+  for (int64_t row = blockIdx.x * (int64_t)WARPS + warp; row < rows;
+       row += (int64_t)gridDim.x * WARPS) {
+    const T* xr = x + row * cols;
+    const T* dyr = dy + row * cols;
+    uint4 xraw[NV], graw[NV], araw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t vi = lane + 32 * i;
+      if (vi < nvec) {
+        xraw[i] = VecIO<T>::load_raw(xr + vi * V);
+        graw[i] = VecIO<T>::load_raw(dyr + vi * V);
+        if (dx_add) araw[i] = VecIO<T>::load_raw(dx_add + row * cols + vi * V);
+      }
+    }
+    const float mu = mean[row], rs = rstd[row];
+    float c1 = 0.0f, c2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t vi = lane + 32 * i;
+      if (vi < nvec) {
+        float xv[V], g[V], ga[V];
+        VecIO<T>::unpack(xraw[i], xv);
+        VecIO<T>::unpack(graw[i], g);
+        load_params<TP, V>(gamma, vi * V, ga);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          const float gg = g[j] * ga[j];
+          c1 += gg;
+          c2 += gg * xh;
+          dg[i][j] += g[j] * xh;
+          db[i][j] += g[j];
+        }
+      }
+    }
+    c1 = warp_sum(c1) / (float)cols;
+    c2 = warp_sum(c2) / (float)cols;
+    T* dxr = dx + row * cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t vi = lane + 32 * i;
+      if (vi < nvec) {
+        float o[V], xv[V], g[V], ga[V];
+        VecIO<T>::unpack(xraw[i], xv);
+        VecIO<T>::unpack(graw[i], g);
+        load_params<TP, V>(gamma, vi * V, ga);
+        if (dx_add) VecIO<T>::unpack(araw[i], o);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float r = rs * (g[j] * ga[j] - c1 - (xv[j] - mu) * rs * c2);
+          o[j] = dx_add ? o[j] + r : r;
+        }
+        VecIO<T>::store(dxr + vi * V, o);
+      }
+    }
+  }
+
+  // ---- fold the CTA's warps in warp order: sh_fold[0][c] = dgamma part, [1][c] = dbeta part
+  for (int w = 0; w < WARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int64_t vi = lane + 32 * i;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const int64_t c = vi * V + j;
+            if (w == 0) { sh_fold[c] = dg[i][j]; sh_fold[cols + c] = db[i][j]; }
+            else { sh_fold[c] += dg[i][j]; sh_fold[cols + c] += db[i][j]; }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const int64_t two = 2 * cols;
+  float* mine = scratch + (int64_t)blockIdx.x * two;
+  for (int64_t c = threadIdx.x; c < two; c += THREADS) mine[c] = sh_fold[c];
+  if (!dgamma || !dbeta) return;
+
+  // ---- last CTA of each group adds the group's partials; last group adds the group sums
+  const int group = blockIdx.x / FB_GROUP;
+  const int ngroups = ((int)gridDim.x + FB_GROUP - 1) / FB_GROUP;
+  const int first = group * FB_GROUP;
+  const int members = min(FB_GROUP, (int)gridDim.x - first);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) sh_last = (atomicAdd(&g_ln_tickets[1 + group], 1u) == (unsigned)(members - 1));
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  float* gsum = scratch + ((int64_t)gridDim.x + group) * two;
+  for (int64_t c = threadIdx.x; c < two; c += THREADS) {
+    float acc = 0.0f;
+    for (int b = 0; b < members; ++b) acc += __ldcg(scratch + (int64_t)(first + b) * two + c);
+    gsum[c] = acc;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    g_ln_tickets[1 + group] = 0;
+    sh_last = (atomicAdd(&g_ln_tickets[0], 1u) == (unsigned)(ngroups - 1));
+  }
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  for (int64_t c = threadIdx.x; c < two; c += THREADS) {
+    float acc = 0.0f;
+    for (int g = 0; g < ngroups; ++g) acc += __ldcg(scratch + ((int64_t)gridDim.x + g) * two + c);
+    if (c < cols) store_grad(dgamma, grad_dtype, c, acc, accumulate);
+    else store_grad(dbeta, grad_dtype, c - cols, acc, accumulate);
+  }
+  if (threadIdx.x == 0) g_ln_tickets[0] = 0;
+}
+
 template <typename T, typename TP>
 __global__ void __launch_bounds__(THREADS)
 ln_bwd_generic(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
@@ -306,7 +490,8 @@ cudaError_t ln_fwd_dispatch(const void* x, const void* gamma, const void* beta, 
   const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
 #define LT_LN_FWD(NVV)                                                                       \
   launch_pdl(ln_fwd_kernel<T, TP, NVV>, dim3(grid), dim3(THREADS), 0, s, (const T*)x,          \
-             (const TP*)gamma, (const TP*)beta, eps, (T*)y, mean, rstd, rows, cols)
+             (const TP*)gamma, (const TP*)beta, eps, (T*)y, mean, rstd, rows, cols, vec_params)
+  const int vec_params = is_aligned16(gamma) && is_aligned16(beta) ? 1 : 0;
   if (fast) {
     const int64_t per_lane = (cols / V + 31) / 32;
     if (per_lane <= 1) LT_LN_FWD(1);
@@ -326,10 +511,32 @@ cudaError_t ln_fwd_dispatch(const void* x, const void* gamma, const void* beta, 
 template <typename T, typename TP>
 cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, const float* mean,
                             const float* rstd, const void* dx_add, void* dx, float* scratch,
-                            int64_t rows, int64_t cols, int* nparts, cudaStream_t s) {
+                            int64_t rows, int64_t cols, int* nparts, void* dgamma, void* dbeta,
+                            int grad_dtype, int accumulate, bool* params_done, cudaStream_t s) {
   constexpr int V = VecIO<T>::N;
   const bool fast = cols % V == 0 && cols <= 32 * 8 * V && is_aligned16(x) && is_aligned16(dy) &&
                     is_aligned16(dx) && (!dx_add || is_aligned16(dx_add));
+  *params_done = false;
+  if (fast && cols <= 32 * 4 * V && is_aligned16(gamma)) {
+    // one kernel: dx, dgamma and dbeta (rows up to 4 vectors per lane keep their partial sums
+    // in registers)
+    const unsigned grid = (unsigned)bwd_blocks(rows);
+    const size_t smem = sizeof(float) * 2 * (size_t)cols;
+#define LT_LN_FUSED(NVV)                                                                      \
+  launch_pdl(ln_bwd_fused_kernel<T, TP, NVV>, dim3(grid), dim3(THREADS), smem, s, (const T*)x,  \
+             (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx, rows, cols,  \
+             scratch, dgamma, dbeta, grad_dtype, accumulate)
+    const int64_t per_lane = (cols / V + 31) / 32;
+    if (per_lane <= 1) LT_LN_FUSED(1);
+    else if (per_lane <= 2) LT_LN_FUSED(2);
+    else if (per_lane <= 3) LT_LN_FUSED(3);
+    else LT_LN_FUSED(4);
+#undef LT_LN_FUSED
+    LT_COUNT_LAUNCH();
+    *params_done = true;
+    *nparts = (int)grid;
+    return cudaGetLastError();
+  }
   if (fast) {
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
 #define LT_LN_BWD(NVV)                                                                       \
@@ -429,7 +636,7 @@ cudaError_t layernorm_forward(int dtype, const void* x, const void* gamma, const
 
 int64_t layernorm_backward_scratch_floats(int64_t rows, int64_t cols) {
   (void)rows;
-  return (int64_t)BWD_MAX_BLOCKS * 2 * cols;
+  return (int64_t)(BWD_MAX_BLOCKS + FB_MAX_GROUPS) * 2 * cols;   // CTA partials + group sums
 }
 
 cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const void* gamma,
@@ -439,15 +646,17 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
                                int64_t cols, cudaStream_t s) {
   if (rows <= 0 || cols <= 0) return cudaSuccess;
   int nparts = 0;
+  bool params_done = false;
   cudaError_t e = cudaErrorInvalidValue;
+  if (grad_dtype != DT_F32 && grad_dtype != DT_BF16 && grad_dtype != DT_F16) return e;
   LT_DISPATCH_DTYPE(dtype, T, {
     LT_DISPATCH_DTYPE(param_dtype, TP, {
       e = ln_bwd_dispatch<T, TP>(x, dy, gamma, mean, rstd, dx_add, dx, scratch, rows, cols,
-                                 &nparts, s);
+                                 &nparts, dgamma, dbeta, grad_dtype, accumulate, &params_done, s);
     })
   })
   if (e != cudaSuccess) return e;
-  if (dgamma && dbeta) {
+  if (dgamma && dbeta && !params_done) {
     LT_DISPATCH_DTYPE(grad_dtype, TG, {
       launch_pdl(ln_param_reduce<TG>, dim3((unsigned)((2 * cols + 31) / 32)), dim3(256), 0, s,
                  scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
