@@ -5,14 +5,15 @@
 // reference kernel reads each row three times from global memory and has no backward at
 // all (csrc/cuda/ops/fused.cu:63-127); its Lua LayerNorm backward walks elements on the
 // CPU (lua/luatorch/nn/layernorm.lua:76-126).
-// Backward: ONE kernel.  Each warp walks rows (x and dy of a row stay in registers between the
-// two passes), writes dx (optionally adding an incoming residual gradient) and accumulates
-// its dgamma / dbeta terms in registers; a CTA folds its warps in warp order through shared
-// memory and writes one partial row to scratch; the last CTA of each group of 16 (a ticket
-// counter) adds the group's partials in CTA order, and the last group to finish adds the
-// group sums in group order and writes dgamma / dbeta.  Every sum has a fixed order, so the
-// result does not depend on timing.  (Rows that the vector path cannot address fall back to
-// separate dx / partial / reduce kernels.)
+// Backward: persistent warps walk rows (x and dy of a row stay in registers between the two
+// passes, the next row's loads are issued before the current row's arithmetic), write dx
+// (optionally adding an incoming residual gradient) and accumulate their dgamma / dbeta terms
+// in registers; a CTA adds its warps in a fixed tree through shared memory and writes one
+// partial row to scratch; a second, small kernel adds the CTA partials in a fixed order
+// (many columns in parallel; doing this inside the first kernel left one CTA walking all
+// partials while every other SM idled).  Every sum has a fixed order, so the result does not
+// depend on timing.  (Rows that the vector path cannot address fall back to separate dx /
+// partial kernels.)
 #include "ops.h"
 #include "common.cuh"
 
@@ -251,62 +252,77 @@ ln_stats_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* 
   }
 }
 
-// Ticket words of the fused backward: [0] groups finished, [1 + g] CTAs of group g finished.
-// They return to zero at the end of every launch.  Launches that can overlap on the GPU
-// (different streams with no dependency) would share them: keep LayerNorm backward calls
-// ordered on one stream.
-constexpr int FB_GROUP = 16;
-constexpr int FB_MAX_GROUPS = (BWD_MAX_BLOCKS + FB_GROUP - 1) / FB_GROUP;
-__device__ unsigned g_ln_tickets[1 + FB_MAX_GROUPS];
+constexpr int FB_WARPS = 4;                 // 128 threads, three CTAs per SM: up to 168 registers a thread
+constexpr int FB_THREADS = FB_WARPS * 32;
+constexpr int FB_MAX_BLOCKS = 3 * 148;
 
-__device__ __forceinline__ void store_grad(void* base, int dtype, int64_t i, float v, int accumulate) {
-  if (dtype == DT_F32) {
-    float* p = static_cast<float*>(base) + i;
-    *p = accumulate ? *p + v : v;
-  } else if (dtype == DT_BF16) {
-    __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base) + i;
-    *p = __float2bfloat16(accumulate ? __bfloat162float(*p) + v : v);
-  } else {
-    __half* p = static_cast<__half*>(base) + i;
-    *p = __float2half(accumulate ? __half2float(*p) + v : v);
-  }
-}
-
+// Persistent warps: a warp walks rows blockIdx.x * 4 + warp, + gridDim.x * 4, ... and loads the
+// NEXT row's x and dy before it works on the current one, so HBM reads, arithmetic and the dx
+// stores of neighbouring rows overlap.  The dgamma / dbeta terms accumulate in registers over
+// all of a warp's rows; at the end the CTA's four warps are added in a fixed binary tree
+// through shared memory (1->0 and 3->2, then 2->0) and warp 0 writes the CTA's partial row to
+// scratch.
 template <typename T, typename TP, int NV>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(FB_THREADS, 3)
 ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
                     const float* __restrict__ mean, const float* __restrict__ rstd,
                     const T* __restrict__ dx_add, T* __restrict__ dx, int64_t rows, int64_t cols,
-                    float* __restrict__ scratch, void* dgamma, void* dbeta, int grad_dtype,
-                    int accumulate) {
+                    float* __restrict__ scratch) {
   pdl_enter();
   constexpr int V = VecIO<T>::N;
-  extern __shared__ float sh_fold[];       // [2][cols]
-  __shared__ int sh_last;
+  __shared__ float sh_fold[(FB_WARPS / 2) * 2 * 32 * VecIO<T>::N];   // [WARPS / 2][2][32 lanes x V]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t nvec = cols / V;
+  const int64_t stride = (int64_t)gridDim.x * FB_WARPS;
   float dg[NV][V], db[NV][V];
 #pragma unroll
   for (int i = 0; i < NV; ++i)
 #pragma unroll
     for (int j = 0; j < V; ++j) { dg[i][j] = 0.0f; db[i][j] = 0.0f; }
 
-  for (int64_t row = blockIdx.x * (int64_t)WARPS + warp; row < rows;
-       row += (int64_t)gridDim.x * WARPS) {
-    const T* xr = x + row * cols;
-    const T* dyr = dy + row * cols;
-    uint4 xraw[NV], graw[NV], araw[NV];
+  int64_t row = blockIdx.x * (int64_t)FB_WARPS + warp;
+  uint4 xraw[NV], graw[NV];
+  float mu = 0.0f, rs = 0.0f;
+  if (row < rows) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
-        xraw[i] = VecIO<T>::load_raw(xr + vi * V);
-        graw[i] = VecIO<T>::load_raw(dyr + vi * V);
-        if (dx_add) araw[i] = VecIO<T>::load_raw(dx_add + row * cols + vi * V);
+        xraw[i] = VecIO<T>::load_raw(x + row * cols + vi * V);
+        graw[i] = VecIO<T>::load_raw(dy + row * cols + vi * V);
       }
     }
-    const float mu = mean[row], rs = rstd[row];
+    mu = mean[row];
+    rs = rstd[row];
+  }
+  while (row < rows) {
+    // ---- the next row's loads go out before this row's arithmetic
+    const int64_t nrow = row + stride;
+    uint4 nx[NV], ng[NV];
+    float nmu = 0.0f, nrs = 0.0f;
+    if (nrow < rows) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int64_t vi = lane + 32 * i;
+        if (vi < nvec) {
+          nx[i] = VecIO<T>::load_raw(x + nrow * cols + vi * V);
+          ng[i] = VecIO<T>::load_raw(dy + nrow * cols + vi * V);
+        }
+      }
+      nmu = mean[nrow];
+      nrs = rstd[nrow];
+    }
+    // this row's residual-stream gradient: requested now, consumed after the two reductions
+    uint4 araw[NV];
+    if (dx_add) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int64_t vi = lane + 32 * i;
+        if (vi < nvec) araw[i] = VecIO<T>::load_raw(dx_add + row * cols + vi * V);
+      }
+    }
     float c1 = 0.0f, c2 = 0.0f;
+    const float shift = -mu * rs;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
@@ -317,11 +333,11 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
         load_params<TP, V>(gamma, vi * V, ga);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float xh = (xv[j] - mu) * rs;
+          const float xh = fmaf(xv[j], rs, shift);
           const float gg = g[j] * ga[j];
           c1 += gg;
-          c2 += gg * xh;
-          dg[i][j] += g[j] * xh;
+          c2 = fmaf(gg, xh, c2);
+          dg[i][j] = fmaf(g[j], xh, dg[i][j]);
           db[i][j] += g[j];
         }
       }
@@ -334,76 +350,63 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
       const int64_t vi = lane + 32 * i;
       if (vi < nvec) {
         float o[V], xv[V], g[V], ga[V];
+        if (dx_add) VecIO<T>::unpack(araw[i], o);
         VecIO<T>::unpack(xraw[i], xv);
         VecIO<T>::unpack(graw[i], g);
         load_params<TP, V>(gamma, vi * V, ga);
-        if (dx_add) VecIO<T>::unpack(araw[i], o);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float r = rs * (g[j] * ga[j] - c1 - (xv[j] - mu) * rs * c2);
+          const float xh = fmaf(xv[j], rs, shift);
+          const float r = rs * (fmaf(g[j], ga[j], -c1) - xh * c2);
           o[j] = dx_add ? o[j] + r : r;
         }
         VecIO<T>::store(dxr + vi * V, o);
       }
     }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) { xraw[i] = nx[i]; graw[i] = ng[i]; }
+    mu = nmu;
+    rs = nrs;
+    row = nrow;
   }
 
-  // ---- fold the CTA's warps in warp order: sh_fold[0][c] = dgamma part, [1][c] = dbeta part
-  for (int w = 0; w < WARPS; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int64_t vi = lane + 32 * i;
-        if (vi < nvec) {
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const int64_t c = vi * V + j;
-            if (w == 0) { sh_fold[c] = dg[i][j]; sh_fold[cols + c] = db[i][j]; }
-            else { sh_fold[c] += dg[i][j]; sh_fold[cols + c] += db[i][j]; }
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
+  // ---- fixed binary tree over the CTA's warps, one 16-byte vector slice at a time
   const int64_t two = 2 * cols;
   float* mine = scratch + (int64_t)blockIdx.x * two;
-  for (int64_t c = threadIdx.x; c < two; c += THREADS) mine[c] = sh_fold[c];
-  if (!dgamma || !dbeta) return;
-
-  // ---- last CTA of each group adds the group's partials; last group adds the group sums
-  const int group = blockIdx.x / FB_GROUP;
-  const int ngroups = ((int)gridDim.x + FB_GROUP - 1) / FB_GROUP;
-  const int first = group * FB_GROUP;
-  const int members = min(FB_GROUP, (int)gridDim.x - first);
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) sh_last = (atomicAdd(&g_ln_tickets[1 + group], 1u) == (unsigned)(members - 1));
-  __syncthreads();
-  if (!sh_last) return;
-  __threadfence();
-  float* gsum = scratch + ((int64_t)gridDim.x + group) * two;
-  for (int64_t c = threadIdx.x; c < two; c += THREADS) {
-    float acc = 0.0f;
-    for (int b = 0; b < members; ++b) acc += __ldcg(scratch + (int64_t)(first + b) * two + c);
-    gsum[c] = acc;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int64_t vi = lane + 32 * i;
+    const bool has = vi < nvec;
+#pragma unroll
+    for (int step = 1; step < FB_WARPS; step <<= 1) {
+      float* slot = sh_fold + (warp / (2 * step)) * (2 * 32 * V);
+      if ((warp & (2 * step - 1)) == step) {          // sender at this level
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          slot[j * 32 + lane] = dg[i][j];             // lanes hit consecutive words
+          slot[32 * V + j * 32 + lane] = db[i][j];
+        }
+      }
+      __syncthreads();
+      if ((warp & (2 * step - 1)) == 0) {             // receiver
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          dg[i][j] += slot[j * 32 + lane];
+          db[i][j] += slot[32 * V + j * 32 + lane];
+        }
+      }
+      __syncthreads();
+    }
+    if (warp == 0 && has) {
+      float4* pg = reinterpret_cast<float4*>(mine + vi * V);
+      float4* pb = reinterpret_cast<float4*>(mine + cols + vi * V);
+#pragma unroll
+      for (int q = 0; q < V / 4; ++q) {
+        pg[q] = make_float4(dg[i][4 * q], dg[i][4 * q + 1], dg[i][4 * q + 2], dg[i][4 * q + 3]);
+        pb[q] = make_float4(db[i][4 * q], db[i][4 * q + 1], db[i][4 * q + 2], db[i][4 * q + 3]);
+      }
+    }
   }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    g_ln_tickets[1 + group] = 0;
-    sh_last = (atomicAdd(&g_ln_tickets[0], 1u) == (unsigned)(ngroups - 1));
-  }
-  __syncthreads();
-  if (!sh_last) return;
-  __threadfence();
-  for (int64_t c = threadIdx.x; c < two; c += THREADS) {
-    float acc = 0.0f;
-    for (int g = 0; g < ngroups; ++g) acc += __ldcg(scratch + ((int64_t)gridDim.x + g) * two + c);
-    if (c < cols) store_grad(dgamma, grad_dtype, c, acc, accumulate);
-    else store_grad(dbeta, grad_dtype, c - cols, acc, accumulate);
-  }
-  if (threadIdx.x == 0) g_ln_tickets[0] = 0;
 }
 
 template <typename T, typename TP>
@@ -452,24 +455,36 @@ ln_param_partials_generic(const T* __restrict__ x, const T* __restrict__ dy,
   scratch[(int64_t)blockIdx.y * 2 * cols + cols + c] = b;
 }
 
-// 32 columns x 8 partial-lanes per block; lanes are folded in a fixed order (reproducible).
+// 32 columns x 32 partial-lanes per block: lane py adds partials py, py + 32, ... (independent
+// loads, 128 bytes per warp and row), then the 32 lanes are folded in a fixed order.
 template <typename TG>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
                 TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate) {
   pdl_enter();
-  __shared__ float sh[8][33];
+  __shared__ float sh[32][33];
   const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
   const int64_t c = blockIdx.x * 32ll + cx;
   float t = 0.0f;
-  if (c < 2 * cols)
-    for (int p = py; p < nparts; p += 8) t += scratch[(int64_t)p * 2 * cols + c];
+  if (c < 2 * cols) {
+    // all of a lane's loads are requested before the first add (fixed order kept)
+    for (int p0 = py; p0 < nparts; p0 += 32 * 16) {
+      float v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const int p = p0 + 32 * k;
+        v[k] = p < nparts ? __ldcg(scratch + (int64_t)p * 2 * cols + c) : 0.0f;
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) t += v[k];
+    }
+  }
   sh[py][cx] = t;
   __syncthreads();
   if (py == 0 && c < 2 * cols) {
     float r = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) r += sh[i][cx];
+    for (int i = 0; i < 32; ++i) r += sh[i][cx];
     TG* dst = c < cols ? dgamma + c : dbeta + (c - cols);
     if (accumulate) r += VecIO<TG>::ld(dst);
     VecIO<TG>::st(dst, r);
@@ -518,14 +533,15 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
                     is_aligned16(dx) && (!dx_add || is_aligned16(dx_add));
   *params_done = false;
   if (fast && cols <= 32 * 4 * V && is_aligned16(gamma)) {
-    // one kernel: dx, dgamma and dbeta (rows up to 4 vectors per lane keep their partial sums
-    // in registers)
-    const unsigned grid = (unsigned)bwd_blocks(rows);
-    const size_t smem = sizeof(float) * 2 * (size_t)cols;
+    // one kernel: dx, dgamma and dbeta (rows up to 4 vectors per lane keep their parameter
+    // sums in registers)
+    const int64_t want = (rows + FB_WARPS - 1) / FB_WARPS;
+    const unsigned grid = (unsigned)(want < FB_MAX_BLOCKS ? want : FB_MAX_BLOCKS);
+    const size_t smem = 0;
 #define LT_LN_FUSED(NVV)                                                                      \
-  launch_pdl(ln_bwd_fused_kernel<T, TP, NVV>, dim3(grid), dim3(THREADS), smem, s, (const T*)x,  \
+  launch_pdl(ln_bwd_fused_kernel<T, TP, NVV>, dim3(grid), dim3(FB_THREADS), smem, s, (const T*)x,  \
              (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx, rows, cols,  \
-             scratch, dgamma, dbeta, grad_dtype, accumulate)
+             scratch)
     const int64_t per_lane = (cols / V + 31) / 32;
     if (per_lane <= 1) LT_LN_FUSED(1);
     else if (per_lane <= 2) LT_LN_FUSED(2);
@@ -533,8 +549,7 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
     else LT_LN_FUSED(4);
 #undef LT_LN_FUSED
     LT_COUNT_LAUNCH();
-    *params_done = true;
-    *nparts = (int)grid;
+    *nparts = (int)grid;     // one partial row per CTA; ln_param_reduce adds them in CTA order
     return cudaGetLastError();
   }
   if (fast) {
@@ -636,7 +651,7 @@ cudaError_t layernorm_forward(int dtype, const void* x, const void* gamma, const
 
 int64_t layernorm_backward_scratch_floats(int64_t rows, int64_t cols) {
   (void)rows;
-  return (int64_t)(BWD_MAX_BLOCKS + FB_MAX_GROUPS) * 2 * cols;   // CTA partials + group sums
+  return (int64_t)FB_MAX_BLOCKS * 2 * cols;   // one partial row per CTA
 }
 
 cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const void* gamma,
@@ -658,7 +673,7 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
   if (e != cudaSuccess) return e;
   if (dgamma && dbeta && !params_done) {
     LT_DISPATCH_DTYPE(grad_dtype, TG, {
-      launch_pdl(ln_param_reduce<TG>, dim3((unsigned)((2 * cols + 31) / 32)), dim3(256), 0, s,
+      launch_pdl(ln_param_reduce<TG>, dim3((unsigned)((2 * cols + 31) / 32)), dim3(1024), 0, s,
                  scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
       LT_COUNT_LAUNCH();
     })
