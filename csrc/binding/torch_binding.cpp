@@ -432,6 +432,29 @@ Tensor layernorm_backward(const Tensor& x, const Tensor& dy, const Tensor& gamma
         "layernorm_backward");
   return dx;
 }
+// The same, and the column sums of dx go to `dxsum` (dtype of dgamma) when the fused kernels
+// can produce them: returns (dx, done).
+std::tuple<Tensor, bool> layernorm_backward_dxsum(const Tensor& x, const Tensor& dy,
+                                                  const Tensor& gamma, const Tensor& mean,
+                                                  const Tensor& rstd, const OptT& dx_add,
+                                                  Tensor& dgamma, Tensor& dbeta, bool accumulate,
+                                                  Tensor& dxsum, bool dxsum_accumulate) {
+  need_cuda_contig(x, "x"); need_cuda_contig(dy, "dy");
+  TORCH_CHECK(dgamma.scalar_type() == dbeta.scalar_type() && dxsum.scalar_type() == dgamma.scalar_type());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t cols = x.size(-1), rows = x.numel() / cols;
+  TORCH_CHECK(dxsum.numel() == cols && dxsum.is_contiguous());
+  Tensor dx = at::empty_like(x);
+  Tensor scratch = scratch_floats(lt::layernorm_backward_scratch_floats(rows, cols), x);
+  int done = 0;
+  check(lt::layernorm_backward(dt(x), x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), dt(gamma),
+                               mean.data_ptr<float>(), rstd.data_ptr<float>(), optptr(dx_add),
+                               dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), dt(dgamma),
+                               accumulate, scratch.data_ptr<float>(), rows, cols, cur_stream(),
+                               dxsum.data_ptr(), dxsum_accumulate ? 1 : 0, &done),
+        "layernorm_backward");
+  return {dx, done != 0};
+}
 Tensor gelu_bias_forward(const Tensor& x, const OptT& bias) {
   need_cuda_contig(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
@@ -759,6 +782,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pointwise_loss_backward", &pointwise_loss_backward);
   m.def("layernorm_forward", &layernorm_forward);
   m.def("layernorm_backward", &layernorm_backward);
+  m.def("layernorm_backward_dxsum", &layernorm_backward_dxsum);
   m.def("gelu_bias_forward", &gelu_bias_forward);
   m.def("gelu_bias_backward", &gelu_bias_backward);
   m.def("embedding_forward", &embedding_forward);

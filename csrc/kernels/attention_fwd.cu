@@ -145,6 +145,7 @@ struct FwdParams {
   __nv_bfloat16* o;
   long long o_sb, o_ss, o_sh;
   float* lse;
+  int tmem_p;        // keep P in tensor memory (A operand of P V read from TMEM)
 };
 
 template <int D>
@@ -518,6 +519,37 @@ __device__ __forceinline__ void v2_chunk_exp_store(const uint32_t (&r)[32], floa
   }
 }
 
+// Same exponentials, but P goes to tensor memory (two bf16 keys per 32-bit column, the layout
+// tcgen05.mma reads an A operand from): 32 scores -> 16 columns starting at `p_addr`.
+__device__ __forceinline__ void v2_chunk_exp_tmem(const uint32_t (&r)[32], float c, float mc,
+                                                  bool masked, int valid, uint32_t p_addr,
+                                                  float2& sum2) {
+  uint32_t packed[16];
+  const float2 cc = make_float2(c, c), mm = make_float2(-mc, -mc);
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const float2 x = ffma2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), cc, mm);
+    float p0 = ex2(x.x), p1 = ex2(x.y);
+    if (masked) {
+      p0 = (i < valid) ? p0 : 0.0f;
+      p1 = (i + 1 < valid) ? p1 : 0.0f;
+    }
+    sum2 = fadd2(sum2, make_float2(p0, p1));
+    __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
+  }
+  tmem_st_32x16(p_addr, packed);
+}
+
+bool use_tmem_p() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LT_FLASH_TMEM_P");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v != 0;
+}
+
 template <int D>
 struct Fwd2Smem {
   static constexpr int DC = D / 64;                          // 64-wide head-dim chunks
@@ -527,7 +559,9 @@ struct Fwd2Smem {
   static constexpr int OFF_V = OFF_K + 2 * TILE;             // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * TILE;             // 128 x 128 bf16 = 2 chunks
   static constexpr int OFF_BAR = OFF_P + 2 * CHUNK_BYTES;
-  static constexpr int TMEM_COLS = 256;                      // 128 scores + D output columns
+  // 128 score columns + D output columns (+ 64 columns of bf16 P when P stays in tensor memory)
+  static constexpr int TMEM_COLS = D == 64 ? 256 : 512;
+  static constexpr int P_COL = 128 + D;
   static constexpr int TOTAL = OFF_BAR + 256;
 };
 
@@ -656,6 +690,14 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         tc_fence_after_sync();
         // O[128 x D] (+)= P[128 x 128 keys] V[128 keys x D]
+        if (p.tmem_p) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {     // 16 keys = 8 TMEM columns of P per step
+            const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * L::TILE) + (ks * 16) * 128;
+            const uint64_t vd = make_smem_desc_sw128(v_addr, CHUNK_BYTES, 1024);
+            umma_bf16_ts(tmem_o, tmem_base + L::P_COL + ks * 8, vd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+        } else
 #pragma unroll
         for (int kc = 0; kc < 2; ++kc) {
           const uint64_t pd = make_smem_desc_sw128(smem_u32(smem + L::OFF_P + kc * CHUNK_BYTES), 16, 1024);
@@ -755,8 +797,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_before_sync();
       mbar_arrive(smem_u32(s_empty));
       const float mc = (m_used == -INFINITY) ? 0.0f : m_used * c;
-      v2_chunk_exp_store(ra, c, mc, need_mask, valid - own_c, p_row, half * 2, row, l2);
-      v2_chunk_exp_store(rb, c, mc, need_mask, valid - own_c - 32, p_row, half * 2 + 1, row, l2);
+      if (p.tmem_p) {
+        const uint32_t p_addr = tmem_base + lane_base + L::P_COL + half * 32;
+        v2_chunk_exp_tmem(ra, c, mc, need_mask, valid - own_c, p_addr, l2);
+        v2_chunk_exp_tmem(rb, c, mc, need_mask, valid - own_c - 32, p_addr + 16, l2);
+        tmem_st_wait();
+      } else {
+        v2_chunk_exp_store(ra, c, mc, need_mask, valid - own_c, p_row, half * 2, row, l2);
+        v2_chunk_exp_store(rb, c, mc, need_mask, valid - own_c - 32, p_row, half * 2 + 1, row, l2);
+      }
       tc_fence_before_sync();
       fence_proxy_async();
       mbar_arrive(smem_u32(p_full));
@@ -832,6 +881,7 @@ cudaError_t launch_fwd_v2(const AttnArgs& a, cudaStream_t stream) {
   p.o = (__nv_bfloat16*)a.o;
   p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
   p.lse = a.lse;
+  p.tmem_p = use_tmem_p() ? 1 : 0;
   dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
   cudaError_t le = launch_pdl(flash_fwd2_kernel<D>, grid, dim3(V2_THREADS), L::TOTAL, stream, tq, tk, tv, p);
   if (le != cudaSuccess) return le;
@@ -871,6 +921,7 @@ cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.o = (__nv_bfloat16*)a.o;
   p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
   p.lse = a.lse;
+  p.tmem_p = 0;
   dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
   cudaError_t le = launch_pdl(flash_fwd_kernel<D>, grid, dim3(NUM_THREADS), L::TOTAL, stream, tq, tk, tv, p);
   if (le != cudaSuccess) return le;

@@ -303,12 +303,23 @@ colsum_fused(const T* __restrict__ in, int64_t ld, int64_t rows, int64_t cols,
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = 0.0f;
   if (ok) {
-#pragma unroll 4
-    for (int64_t r = r0 + warp; r < r1; r += 8) {
-      float v[V];
-      VecIO<T>::load(in + r * ld + c0, v);
+    // eight rows requested at a time, added in row order
+    for (int64_t rb = r0 + warp; rb < r1; rb += 8 * 8) {
+      uint4 raw[8];
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] += v[j];
+      for (int k = 0; k < 8; ++k) {
+        const int64_t r = rb + 8 * k;
+        if (r < r1) raw[k] = VecIO<T>::load_raw(in + r * ld + c0);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (rb + 8 * k < r1) {
+          float v[V];
+          VecIO<T>::unpack(raw[k], v);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += v[j];
+        }
+      }
     }
   }
 #pragma unroll
@@ -336,8 +347,14 @@ colsum_fused(const T* __restrict__ in, int64_t ld, int64_t rows, int64_t cols,
     const int64_t col = gcol0 + c;
     if (col < cols) {
       float t = 0.0f;
-      for (unsigned int sidx = 0; sidx < gridDim.y; ++sidx)
-        t += __ldcg(scratch + (int64_t)sidx * cols + col);
+      for (unsigned int s0 = 0; s0 < gridDim.y; s0 += 16) {   // 16 loads in flight, slab order kept
+        float v[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          v[k] = s0 + k < gridDim.y ? __ldcg(scratch + (int64_t)(s0 + k) * cols + col) : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) t += v[k];
+      }
       if (accumulate) t += VecIO<TO>::ld(out + col);
       VecIO<TO>::st(out + col, t);
     }

@@ -262,23 +262,29 @@ constexpr int FB_MAX_BLOCKS = 3 * 148;
 // all of a warp's rows; at the end the CTA's four warps are added in a fixed binary tree
 // through shared memory (1->0 and 3->2, then 2->0) and warp 0 writes the CTA's partial row to
 // scratch.
-template <typename T, typename TP, int NV>
-__global__ void __launch_bounds__(FB_THREADS, 3)
+template <typename T, typename TP, int NV, bool DXS>
+__global__ void __launch_bounds__(FB_THREADS, (DXS && NV >= 3) ? 2 : 3)
 ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
                     const float* __restrict__ mean, const float* __restrict__ rstd,
                     const T* __restrict__ dx_add, T* __restrict__ dx, int64_t rows, int64_t cols,
                     float* __restrict__ scratch) {
   pdl_enter();
   constexpr int V = VecIO<T>::N;
-  __shared__ float sh_fold[(FB_WARPS / 2) * 2 * 32 * VecIO<T>::N];   // [WARPS / 2][2][32 lanes x V]
+  __shared__ float sh_fold[(FB_WARPS / 2) * (DXS ? 3 : 2) * 32 * VecIO<T>::N];   // [WARPS / 2][sets][32 lanes x V]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t nvec = cols / V;
   const int64_t stride = (int64_t)gridDim.x * FB_WARPS;
-  float dg[NV][V], db[NV][V];
+  // DXS: also the column sums of dx itself (the bias gradient of the linear layer whose output
+  // this LayerNorm normalised), a third set of partial sums
+  constexpr int NS = DXS ? 3 : 2;
+  float dg[NV][V], db[NV][V], dxs[DXS ? NV : 1][V];
 #pragma unroll
   for (int i = 0; i < NV; ++i)
 #pragma unroll
-    for (int j = 0; j < V; ++j) { dg[i][j] = 0.0f; db[i][j] = 0.0f; }
+    for (int j = 0; j < V; ++j) {
+      dg[i][j] = 0.0f; db[i][j] = 0.0f;
+      if (DXS) dxs[i][j] = 0.0f;
+    }
 
   int64_t row = blockIdx.x * (int64_t)FB_WARPS + warp;
   uint4 xraw[NV], graw[NV];
@@ -359,6 +365,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
           const float xh = fmaf(xv[j], rs, shift);
           const float r = rs * (fmaf(g[j], ga[j], -c1) - xh * c2);
           o[j] = dx_add ? o[j] + r : r;
+          if (DXS) dxs[i][j] += o[j];
         }
         VecIO<T>::store(dxr + vi * V, o);
       }
@@ -371,20 +378,21 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
   }
 
   // ---- fixed binary tree over the CTA's warps, one 16-byte vector slice at a time
-  const int64_t two = 2 * cols;
-  float* mine = scratch + (int64_t)blockIdx.x * two;
+  const int64_t rowlen = NS * cols;
+  float* mine = scratch + (int64_t)blockIdx.x * rowlen;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int64_t vi = lane + 32 * i;
     const bool has = vi < nvec;
 #pragma unroll
     for (int step = 1; step < FB_WARPS; step <<= 1) {
-      float* slot = sh_fold + (warp / (2 * step)) * (2 * 32 * V);
+      float* slot = sh_fold + (warp / (2 * step)) * (NS * 32 * V);
       if ((warp & (2 * step - 1)) == step) {          // sender at this level
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           slot[j * 32 + lane] = dg[i][j];             // lanes hit consecutive words
           slot[32 * V + j * 32 + lane] = db[i][j];
+          if (DXS) slot[2 * 32 * V + j * 32 + lane] = dxs[i][j];
         }
       }
       __syncthreads();
@@ -393,6 +401,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
         for (int j = 0; j < V; ++j) {
           dg[i][j] += slot[j * 32 + lane];
           db[i][j] += slot[32 * V + j * 32 + lane];
+          if (DXS) dxs[i][j] += slot[2 * 32 * V + j * 32 + lane];
         }
       }
       __syncthreads();
@@ -404,6 +413,12 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
       for (int q = 0; q < V / 4; ++q) {
         pg[q] = make_float4(dg[i][4 * q], dg[i][4 * q + 1], dg[i][4 * q + 2], dg[i][4 * q + 3]);
         pb[q] = make_float4(db[i][4 * q], db[i][4 * q + 1], db[i][4 * q + 2], db[i][4 * q + 3]);
+      }
+      if (DXS) {
+        float4* ps = reinterpret_cast<float4*>(mine + 2 * cols + vi * V);
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q)
+          ps[q] = make_float4(dxs[i][4 * q], dxs[i][4 * q + 1], dxs[i][4 * q + 2], dxs[i][4 * q + 3]);
       }
     }
   }
@@ -459,21 +474,23 @@ ln_param_partials_generic(const T* __restrict__ x, const T* __restrict__ dy,
 // loads, 128 bytes per warp and row), then the 32 lanes are folded in a fixed order.
 template <typename TG>
 __global__ void __launch_bounds__(1024)
-ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
-                TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate) {
+ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols, int nsets,
+                TG* __restrict__ dgamma, TG* __restrict__ dbeta, int accumulate,
+                TG* __restrict__ dxsum, int dxsum_accumulate) {
   pdl_enter();
   __shared__ float sh[32][33];
   const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
   const int64_t c = blockIdx.x * 32ll + cx;
+  const int64_t rowlen = (int64_t)nsets * cols;
   float t = 0.0f;
-  if (c < 2 * cols) {
+  if (c < rowlen) {
     // all of a lane's loads are requested before the first add (fixed order kept)
     for (int p0 = py; p0 < nparts; p0 += 32 * 16) {
       float v[16];
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
         const int p = p0 + 32 * k;
-        v[k] = p < nparts ? __ldcg(scratch + (int64_t)p * 2 * cols + c) : 0.0f;
+        v[k] = p < nparts ? __ldcg(scratch + (int64_t)p * rowlen + c) : 0.0f;
       }
 #pragma unroll
       for (int k = 0; k < 16; ++k) t += v[k];
@@ -481,12 +498,16 @@ ln_param_reduce(const float* __restrict__ scratch, int nparts, int64_t cols,
   }
   sh[py][cx] = t;
   __syncthreads();
-  if (py == 0 && c < 2 * cols) {
+  if (py == 0 && c < rowlen) {
     float r = 0.0f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) r += sh[i][cx];
-    TG* dst = c < cols ? dgamma + c : dbeta + (c - cols);
-    if (accumulate) r += VecIO<TG>::ld(dst);
+    TG* dst;
+    int acc;
+    if (c < cols) { dst = dgamma + c; acc = accumulate; }
+    else if (c < 2 * cols) { dst = dbeta + (c - cols); acc = accumulate; }
+    else { dst = dxsum + (c - 2 * cols); acc = dxsum_accumulate; }
+    if (acc) r += VecIO<TG>::ld(dst);
     VecIO<TG>::st(dst, r);
   }
 }
@@ -526,27 +547,35 @@ cudaError_t ln_fwd_dispatch(const void* x, const void* gamma, const void* beta, 
 template <typename T, typename TP>
 cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, const float* mean,
                             const float* rstd, const void* dx_add, void* dx, float* scratch,
-                            int64_t rows, int64_t cols, int* nparts, void* dgamma, void* dbeta,
-                            int grad_dtype, int accumulate, bool* params_done, cudaStream_t s) {
+                            int64_t rows, int64_t cols, int* nparts, bool want_dxsum,
+                            bool* dxsum_done, cudaStream_t s) {
   constexpr int V = VecIO<T>::N;
   const bool fast = cols % V == 0 && cols <= 32 * 8 * V && is_aligned16(x) && is_aligned16(dy) &&
                     is_aligned16(dx) && (!dx_add || is_aligned16(dx_add));
-  *params_done = false;
+  *dxsum_done = false;
   if (fast && cols <= 32 * 4 * V && is_aligned16(gamma)) {
     // one kernel: dx, dgamma and dbeta (rows up to 4 vectors per lane keep their parameter
     // sums in registers)
     const int64_t want = (rows + FB_WARPS - 1) / FB_WARPS;
     const unsigned grid = (unsigned)(want < FB_MAX_BLOCKS ? want : FB_MAX_BLOCKS);
     const size_t smem = 0;
-#define LT_LN_FUSED(NVV)                                                                      \
-  launch_pdl(ln_bwd_fused_kernel<T, TP, NVV>, dim3(grid), dim3(FB_THREADS), smem, s, (const T*)x,  \
-             (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx, rows, cols,  \
-             scratch)
+#define LT_LN_FUSED(NVV, DXSV)                                                                \
+  launch_pdl(ln_bwd_fused_kernel<T, TP, NVV, DXSV>, dim3(grid), dim3(FB_THREADS), smem, s,       \
+             (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx,  \
+             rows, cols, scratch)
     const int64_t per_lane = (cols / V + 31) / 32;
-    if (per_lane <= 1) LT_LN_FUSED(1);
-    else if (per_lane <= 2) LT_LN_FUSED(2);
-    else if (per_lane <= 3) LT_LN_FUSED(3);
-    else LT_LN_FUSED(4);
+    const bool dxs = want_dxsum && per_lane <= 3;   // a third register set fits up to 3 vectors a lane
+    if (dxs) {
+      if (per_lane <= 1) LT_LN_FUSED(1, true);
+      else if (per_lane <= 2) LT_LN_FUSED(2, true);
+      else LT_LN_FUSED(3, true);
+      *dxsum_done = true;
+    } else {
+      if (per_lane <= 1) LT_LN_FUSED(1, false);
+      else if (per_lane <= 2) LT_LN_FUSED(2, false);
+      else if (per_lane <= 3) LT_LN_FUSED(3, false);
+      else LT_LN_FUSED(4, false);
+    }
 #undef LT_LN_FUSED
     LT_COUNT_LAUNCH();
     *nparts = (int)grid;     // one partial row per CTA; ln_param_reduce adds them in CTA order
@@ -651,32 +680,38 @@ cudaError_t layernorm_forward(int dtype, const void* x, const void* gamma, const
 
 int64_t layernorm_backward_scratch_floats(int64_t rows, int64_t cols) {
   (void)rows;
-  return (int64_t)FB_MAX_BLOCKS * 2 * cols;   // one partial row per CTA
+  return (int64_t)FB_MAX_BLOCKS * 3 * cols;   // one partial row (dgamma, dbeta, dx sums) per CTA
 }
 
 cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const void* gamma,
                                int param_dtype, const float* mean, const float* rstd,
                                const void* dx_add, void* dx, void* dgamma, void* dbeta,
                                int grad_dtype, int accumulate, float* scratch, int64_t rows,
-                               int64_t cols, cudaStream_t s) {
+                               int64_t cols, cudaStream_t s, void* dxsum, int dxsum_accumulate,
+                               int* dxsum_done) {
+  if (dxsum_done) *dxsum_done = 0;
   if (rows <= 0 || cols <= 0) return cudaSuccess;
   int nparts = 0;
-  bool params_done = false;
+  bool dxs_done = false;
   cudaError_t e = cudaErrorInvalidValue;
   if (grad_dtype != DT_F32 && grad_dtype != DT_BF16 && grad_dtype != DT_F16) return e;
+  const bool want_dxsum = dxsum != nullptr && dgamma != nullptr && dbeta != nullptr;
   LT_DISPATCH_DTYPE(dtype, T, {
     LT_DISPATCH_DTYPE(param_dtype, TP, {
       e = ln_bwd_dispatch<T, TP>(x, dy, gamma, mean, rstd, dx_add, dx, scratch, rows, cols,
-                                 &nparts, dgamma, dbeta, grad_dtype, accumulate, &params_done, s);
+                                 &nparts, want_dxsum, &dxs_done, s);
     })
   })
   if (e != cudaSuccess) return e;
-  if (dgamma && dbeta && !params_done) {
+  if (dgamma && dbeta) {
+    const int nsets = dxs_done ? 3 : 2;
     LT_DISPATCH_DTYPE(grad_dtype, TG, {
-      launch_pdl(ln_param_reduce<TG>, dim3((unsigned)((2 * cols + 31) / 32)), dim3(1024), 0, s,
-                 scratch, nparts, cols, (TG*)dgamma, (TG*)dbeta, accumulate);
+      launch_pdl(ln_param_reduce<TG>, dim3((unsigned)((nsets * cols + 31) / 32)), dim3(1024), 0, s,
+                 scratch, nparts, cols, nsets, (TG*)dgamma, (TG*)dbeta, accumulate, (TG*)dxsum,
+                 dxsum_accumulate);
       LT_COUNT_LAUNCH();
     })
+    if (dxsum_done) *dxsum_done = dxs_done ? 1 : 0;
   }
   return cudaGetLastError();
 }

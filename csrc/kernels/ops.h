@@ -101,13 +101,17 @@ cudaError_t layernorm_forward(int dtype, const void* x, const void* gamma, const
                               int param_dtype, float eps, void* y, float* mean, float* rstd,
                               int64_t rows, int64_t cols, cudaStream_t s);
 // dx (+= dx_add if given); dgamma/dbeta partial sums land in scratch then are reduced into
-// dgamma/dbeta (dtype grad_dtype, accumulate flag).
+// dgamma/dbeta (dtype grad_dtype, accumulate flag).  `dxsum` (same dtype, own accumulate
+// flag): when given and the fused path applies, the column sums of dx are produced by the same
+// two launches (*dxsum_done = 1) - the bias gradient of a linear layer whose output, plus a
+// residual, was this LayerNorm's input; otherwise *dxsum_done = 0 and the caller sums dx.
 int64_t layernorm_backward_scratch_floats(int64_t rows, int64_t cols);
 cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const void* gamma,
                                int param_dtype, const float* mean, const float* rstd,
                                const void* dx_add, void* dx, void* dgamma, void* dbeta,
                                int grad_dtype, int accumulate, float* scratch, int64_t rows,
-                               int64_t cols, cudaStream_t s);
+                               int64_t cols, cudaStream_t s, void* dxsum = nullptr,
+                               int dxsum_accumulate = 0, int* dxsum_done = nullptr);
 cudaError_t gelu_bias_forward(int dtype, const void* x, const void* bias, int bias_dtype,
                               void* out, int64_t rows, int64_t cols, cudaStream_t s);
 // dx = dy * gelu'(x + bias)

@@ -12,11 +12,28 @@ from ..tensor import Tensor
 from .module import Module, compute_view, param
 
 
-def layernorm_backward_into(x, dy, gamma_view, mean, rstd, gamma_p, beta_p, dx_add=None):
+def layernorm_backward_into(x, dy, gamma_view, mean, rstd, gamma_p, beta_p, dx_add=None,
+                            bias_src=None):
     """dx plus in-place (or accumulated) parameter gradients; shared with the fused
-    transformer block."""
+    transformer block.  `bias_src` = [bias parameter, done flag] of the Linear whose output
+    (plus residual) was normalised: dx is then the complete gradient of that output, and the
+    kernels that write dx also sum its columns into the bias gradient."""
     gbuf, gacc = autograd.grad_target(gamma_p)
     bbuf, bacc = autograd.grad_target(beta_p)
+    if (bias_src is not None and x.is_cuda and gbuf is not None and bbuf is not None
+            and gacc == bacc):
+        bias_p, flag = bias_src
+        sbuf, sacc = autograd.grad_target(bias_p)
+        if sbuf is not None and sbuf.dtype == gbuf.dtype and sbuf.is_contiguous() and not flag[0]:
+            dx, done = B.ext().layernorm_backward_dxsum(
+                B._k(x), B._k(dy), B._k(gamma_view), mean, rstd,
+                None if dx_add is None else B._k(dx_add), gbuf, bbuf, gacc, sbuf, sacc)
+            autograd.grad_written(gamma_p)
+            autograd.grad_written(beta_p)
+            if done:
+                autograd.grad_written(bias_p)
+                flag[0] = True
+            return dx
     if gbuf is not None and bbuf is not None and gacc == bacc:
         dx = B.layernorm_backward(x, dy, gamma_view, mean, rstd, gbuf, bbuf, gacc, dx_add)
         autograd.grad_written(gamma_p)
@@ -49,6 +66,14 @@ class LayerNorm(Module):
         y, mean, rstd = B.layernorm(x, g, b, self.eps)
         out = Tensor(_data=y)
         gamma, beta = self.gamma, self.beta
+        # The bias gradient of the Linear that produced `input` may ride on this backward only
+        # if this LayerNorm is the FIRST consumer of `input` (its backward then runs after
+        # every other consumer's, when input's gradient is complete): true exactly when the
+        # node that produced `input` is still the last one on the tape.
+        bias_src = None
+        if (input._bias_src is not None and autograd.graph and input._node is not None
+                and autograd.graph[-1] is input._node):
+            bias_src = input._bias_src
 
         def grad_fn(grad):
             dy = grad._t if grad._t.dtype == x.dtype else grad._t.to(x.dtype)
@@ -58,7 +83,11 @@ class LayerNorm(Module):
             if (input.requires_grad and input.grad is not None and input._grad_buf is None
                     and input.grad._t.dtype == x.dtype and input.grad._t.shape == x.shape):
                 prior = input.grad._t
-            dx = layernorm_backward_into(x, dy, g, mean, rstd, gamma, beta, dx_add=prior)
+            # dx is the whole gradient of `input` when nothing else contributed, or when the
+            # other contribution is added inside the kernel
+            whole = input.requires_grad and (prior is not None or input.grad is None)
+            dx = layernorm_backward_into(x, dy, g, mean, rstd, gamma, beta, dx_add=prior,
+                                         bias_src=bias_src if whole else None)
             if input.requires_grad:
                 if prior is not None:
                     input.grad = Tensor(_data=dx)

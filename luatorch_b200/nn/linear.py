@@ -120,6 +120,13 @@ class Linear(Module):
         out = Tensor(_data=y)
         if pre is not None:
             out._act_ctx = [act, pre, False]
+        # out = x W + b + residual: the bias gradient is the column sum of out's gradient.  A
+        # LayerNorm that consumes `out` first produces that very gradient in its backward
+        # kernel and can sum its columns on the way (nn/layernorm.py); it then sets the flag.
+        bias_folded = [False]
+        if (residual is not None and act is None and self.use_bias and autograd.enabled
+                and self.bias.requires_grad):
+            out._bias_src = [self.bias, bias_folded]
         fuse_dact = (sole_consumer and input._act_ctx is not None and storage is None
                      and input._act_ctx[1].is_contiguous())
         weight, bias_p = (storage if storage is not None else self.weight), self.bias
@@ -148,7 +155,7 @@ class Linear(Module):
                                                                accumulate=acc, n_valid=N))
                 if view_param is not None:
                     view_param.grad = Tensor(_data=weight.grad._t[:, :N])
-            if bias_p is not None and bias_p.requires_grad:
+            if bias_p is not None and bias_p.requires_grad and not bias_folded[0]:
                 write_param_grad(bias_p, lambda o, acc: B.column_sum(gt, o, acc))
 
         autograd.record("linear", [input, weight, bias_p, residual, view_param], out, grad_fn)

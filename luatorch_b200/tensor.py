@@ -44,7 +44,7 @@ class Tensor:
     """Dense tensor with the reference's object surface (`shape`, `ndim`, `dtype`, `device`)."""
 
     __slots__ = ("_t", "requires_grad", "grad", "_node", "_grad_buf", "_compute", "_hook", "name",
-                 "_unit", "_base", "_base_slice", "_act_ctx")
+                 "_unit", "_base", "_base_slice", "_act_ctx", "_bias_src")
 
     def __init__(self, shape=None, dtype: str = "float32", device: str = "cpu", _data=None):
         if _data is not None:
@@ -65,6 +65,8 @@ class Tensor:
         self._base = None         # fused parameter this tensor is a column slice of
         self._base_slice = None
         self._act_ctx = None      # (activation, pre-activation) of a fused Linear output
+        self._bias_src = None     # [bias parameter, done flag] of the Linear that produced this
+                                  # tensor with a fused residual add (see nn/layernorm.py)
 
     # ------------------------------------------------------------------ construction
     @staticmethod

@@ -281,6 +281,17 @@ def test_layernorm(C, rows, cols, dtype):
     dg2, db2 = torch.zeros_like(dg), torch.zeros_like(db)
     C.layernorm_backward(x, dy, g, mean, rstd, None, dg2, db2, False)
     assert torch.equal(dg, dg2) and torch.equal(db, db2)  # reproducible
+    # the same launches can also sum the columns of dx (bias gradient of the producing Linear)
+    dg3, db3 = torch.zeros_like(dg), torch.zeros_like(db)
+    dxs = torch.full((cols,), 2.0, device="cuda")
+    dx3, done = C.layernorm_backward_dxsum(x, dy, g, mean, rstd, add, dg3, db3, False, dxs, True)
+    assert torch.equal(dx3, dx) and torch.equal(dg3, dg) and torch.equal(db3, db)
+    if done:      # shapes the fused kernels cover; otherwise the caller sums dx itself
+        want = (xf.grad + add.float()).sum(0) + 2.0
+        torch.testing.assert_close(dxs, want, atol=1e-3 * rows ** 0.5 if dtype == torch.float32 else 0.3,
+                                   rtol=1e-3 if dtype == torch.float32 else 3e-2)
+    else:
+        assert torch.all(dxs == 2.0)
 
 
 def test_gelu_bias(C):
