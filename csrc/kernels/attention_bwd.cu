@@ -479,6 +479,333 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
+// =====================================================================================
+// Second-generation backward kernels (head dim 64, sequence length a multiple of 128).
+//
+// The row index of the STATIONARY operand sits on the TMEM lanes, the streamed operand arrives
+// in sub-tiles of 64 rows that become the columns:
+//   DKDV = true : lanes = 128 keys of this CTA, columns = 64 queries per step
+//                 S^T = K Q^T, dP^T = V dO^T; thread (key) rebuilds P^T and dS^T for its row;
+//                 dV += P^T dO and dK += dS^T Q
+//   DKDV = false: lanes = 128 queries of this CTA, columns = 64 keys per step
+//                 S = Q K^T, dP = dO V^T; thread (query) rebuilds dS; dQ += dS K
+// In both cases the rebuilt P / dS tile is exactly the A operand (M = lanes, K = the 64
+// streamed rows) of the accumulating MMAs, so it is written back to tensor memory as packed
+// bf16 (over the columns its fp32 source occupied) and read from there by tcgen05.mma: no
+// shared-memory staging of P or dS, no proxy fences.  A CTA needs 128 + 2 x 64 TMEM columns
+// and 80 KB of shared memory, so two CTAs share an SM and one CTA's exponentials run under
+// the other's MMAs.
+// =====================================================================================
+constexpr int SUB = 64;                         // streamed rows per step
+constexpr int SUB_CHUNK = SUB * 128;            // 64 rows x 64 bf16
+constexpr int B2_THREADS = 64 + 32 * COMPUTE_WARPS;
+
+template <int D>
+struct Bwd2Smem {
+  static constexpr int DC = D / 64;
+  static constexpr int FIX = DC * CHUNK_BYTES;            // one [128 x D] stationary operand
+  static constexpr int STR = DC * SUB_CHUNK;              // one [64 x D] streamed operand
+  static constexpr int STAGES = 3;
+  static constexpr int OFF_FIX0 = 0;
+  static constexpr int OFF_FIX1 = FIX;
+  static constexpr int OFF_STR = 2 * FIX;                 // [stage][2][STR]
+  static constexpr int OFF_BAR = OFF_STR + STAGES * 2 * STR;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr int TMEM_COLS = 128 + 2 * D <= 256 ? 256 : 512;
+};
+
+// 16 columns of one lane's row: scores s and dp (fp32 from TMEM) -> packed bf16 P and dS.
+// lse2 / dsc: log2-domain log-sum-exp and delta * scale, per column (COLV) or for the lane.
+template <bool COLV, bool MASKED>
+__device__ __forceinline__ void rebuild16(const uint32_t (&s)[16], const uint32_t (&dp)[16],
+                                          const float* lse2_c, const float* dsc_c, float lse2_l,
+                                          float dsc_l, float c, float scale, int lo, int hi,
+                                          uint32_t (&pp)[8], uint32_t (&dd)[8]) {
+  // columns j with lo <= j < hi are inside the causal / sequence bounds (only when MASKED)
+  const float2 cc = make_float2(c, c), ss = make_float2(scale, scale);
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float2 ll = COLV ? make_float2(-lse2_c[i], -lse2_c[i + 1]) : make_float2(-lse2_l, -lse2_l);
+    const float2 dl = COLV ? make_float2(-dsc_c[i], -dsc_c[i + 1]) : make_float2(-dsc_l, -dsc_l);
+    const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), cc, ll);
+    float2 pv = make_float2(ex2(x.x), ex2(x.y));
+    if (MASKED) {
+      pv.x = (i >= lo && i < hi) ? pv.x : 0.0f;
+      pv.y = (i + 1 >= lo && i + 1 < hi) ? pv.y : 0.0f;
+    }
+    const float2 g = ffma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ss, dl);
+    const float2 dv = fmul2(pv, g);
+    __nv_bfloat162 hp = __floats2bfloat162_rn(pv.x, pv.y), hd = __floats2bfloat162_rn(dv.x, dv.y);
+    pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
+    dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
+  }
+}
+
+template <int D, bool DKDV>
+__global__ void __launch_bounds__(B2_THREADS, (D == 64 ? 2 : 1))
+flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_constant__ CUtensorMap tm_fix1,
+                  const __grid_constant__ CUtensorMap tm_str0, const __grid_constant__ CUtensorMap tm_str1,
+                  const BwdParams p) {
+  // DKDV: fix0 = K, fix1 = V (128-row boxes), str0 = Q, str1 = dO (64-row boxes)
+  // dQ  : fix0 = Q, fix1 = dO,                 str0 = K, str1 = V
+  using L = Bwd2Smem<D>;
+  constexpr int DC = L::DC, ST = L::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* fix_full = bars;           // 1
+  uint64_t* str_full = bars + 1;       // ST
+  uint64_t* str_empty = bars + 1 + ST; // ST
+  uint64_t* s_full = bars + 1 + 2 * ST;    // S and dP of a step are in TMEM
+  uint64_t* pds_full = bars + 2 + 2 * ST;  // P / dS of a step are back in TMEM
+  uint64_t* acc_full = bars + 3 + 2 * ST;  // final accumulators
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 4 + 2 * ST);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_sub = p.S / SUB;
+  const int own = DKDV ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;  // longest first
+  const int it_begin = DKDV ? (p.causal ? 2 * own : 0) : 0;
+  const int it_end = DKDV ? n_sub : (p.causal ? 2 * own + 2 : n_sub);
+  const int n_it = it_end - it_begin;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(smem_u32(fix_full), 1);
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(smem_u32(&str_full[i]), 1);
+      mbar_init(smem_u32(&str_empty[i]), 1);
+    }
+    mbar_init(smem_u32(s_full), 1);
+    mbar_init(smem_u32(pds_full), 32 * COMPUTE_WARPS);
+    mbar_init(smem_u32(acc_full), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_fix0);
+    tma_prefetch_desc(&tm_fix1);
+    tma_prefetch_desc(&tm_str0);
+    tma_prefetch_desc(&tm_str1);
+  }
+  if (warp_idx == 1) {
+    tmem_alloc(smem_u32(tmem_holder), L::TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_trigger();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();   // operands come from earlier kernels of the stream
+  const uint32_t tmem_s = tmem_base;             // 64 fp32 score columns; packed P lands in them
+  const uint32_t tmem_dp = tmem_base + 64;       // 64 fp32 dP columns; packed dS lands in them
+  const uint32_t tmem_acc0 = tmem_base + 128;    // dK (DKDV) or dQ: from dS
+  const uint32_t tmem_acc1 = tmem_base + 128 + D;  // dV (DKDV only): from P
+  // packed bf16 operand columns: the 32 columns owned by compute half hh keep 16 packed
+  // columns at the start of their own fp32 range (so the two halves never touch each other's)
+  auto packed_col = [](int ks) { return (ks >> 1) * 32 + (ks & 1) * 8; };  // 16 rows of K per step
+
+  auto str0 = [&](int st) { return smem + L::OFF_STR + st * 2 * L::STR; };
+  auto str1 = [&](int st) { return smem + L::OFF_STR + st * 2 * L::STR + L::STR; };
+
+  if (warp_idx == 0) {
+    if (lane == 0) {
+      const uint32_t fb = smem_u32(fix_full);
+      mbar_arrive_expect_tx(fb, 2 * L::FIX);
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        tma_load_4d(smem_u32(smem + L::OFF_FIX0 + c * CHUNK_BYTES), &tm_fix0, fb, 64 * c, own * BT, h, b);
+        tma_load_4d(smem_u32(smem + L::OFF_FIX1 + c * CHUNK_BYTES), &tm_fix1, fb, 64 * c, own * BT, h, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % ST, use = it / ST, t = it_begin + it;
+        if (!mbar_wait_bounded(smem_u32(&str_empty[st]), (use & 1) ^ 1, abort_flag, &g_attn_error, 71))
+          break;
+        const uint32_t sb = smem_u32(&str_full[st]);
+        mbar_arrive_expect_tx(sb, 2 * L::STR);
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          tma_load_4d(smem_u32(str0(st) + c * SUB_CHUNK), &tm_str0, sb, 64 * c, t * SUB, h, b);
+          tma_load_4d(smem_u32(str1(st) + c * SUB_CHUNK), &tm_str1, sb, 64 * c, t * SUB, h, b);
+        }
+      }
+    }
+  } else if (warp_idx == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BT, SUB, 0, 0);   // [128 lanes] x [64 streamed rows]
+      const uint32_t idesc_acc = make_idesc_bf16(BT, D, 0, 1);   // A from TMEM, B = streamed tile, rows as K
+      bool ok = mbar_wait_bounded(smem_u32(fix_full), 0, abort_flag, &g_attn_error, 72);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % ST, use = it / ST;
+        if (!mbar_wait_bounded(smem_u32(&str_full[st]), use & 1, abort_flag, &g_attn_error, 73)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // scores: lanes x streamed rows, contraction over the head dim.  They overwrite the
+        // packed operands of the previous step, which the in-order tensor pipe has consumed
+        // by then (the accumulating MMAs below were issued before these).
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          const uint64_t f0 = make_smem_desc_sw128(smem_u32(smem + L::OFF_FIX0 + c * CHUNK_BYTES), 16, 1024);
+          const uint64_t s0 = make_smem_desc_sw128(smem_u32(str0(st) + c * SUB_CHUNK), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(tmem_s, f0 + (uint64_t)(ks * 2), s0 + (uint64_t)(ks * 2), idesc_s,
+                      (c > 0 || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          const uint64_t f1 = make_smem_desc_sw128(smem_u32(smem + L::OFF_FIX1 + c * CHUNK_BYTES), 16, 1024);
+          const uint64_t s1 = make_smem_desc_sw128(smem_u32(str1(st) + c * SUB_CHUNK), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(tmem_dp, f1 + (uint64_t)(ks * 2), s1 + (uint64_t)(ks * 2), idesc_s,
+                      (c > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(s_full));
+        if (!mbar_wait_bounded(smem_u32(pds_full), it & 1, abort_flag, &g_attn_error, 74)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // accumulate over the 64 streamed rows (K), 16 rows = 2048 bytes of the tile per step
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          // dS-based product: B = streamed operand 0 (Q for dK, K for dQ), its rows as K
+          const uint64_t bd = make_smem_desc_sw128(smem_u32(str0(st)) + ks * 2048, SUB_CHUNK, 1024);
+          umma_bf16_ts(tmem_acc0, tmem_dp + packed_col(ks), bd, idesc_acc, (it > 0 || ks > 0) ? 1u : 0u);
+        }
+        if (DKDV) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t bd = make_smem_desc_sw128(smem_u32(str1(st)) + ks * 2048, SUB_CHUNK, 1024);
+            umma_bf16_ts(tmem_acc1, tmem_s + packed_col(ks), bd, idesc_acc, (it > 0 || ks > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(&str_empty[st]));
+      }
+      if (ok) umma_commit(smem_u32(acc_full));
+    }
+  } else {
+    const int quad = warp_idx & 3;
+    const int hh = (warp_idx - 2) >> 2;          // which 32 of the 64 columns
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    const int row_g = own * BT + row;            // key index (DKDV) or query index
+    const long long bh = ((long long)b * p.H + h) * p.S;
+    float lse2_l = 0.0f, dsc_l = 0.0f;
+    if (!DKDV) {
+      lse2_l = p.lse[bh + row_g] * LOG2E;
+      dsc_l = p.delta[bh + row_g] * p.scale;
+    }
+    bool ok = true;
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int t = it_begin + it;
+      const int c0 = t * SUB + hh * 32;          // global index of this thread's first column
+      // causal bounds in units of this thread's 32 columns
+      int lo = 0, hi = 32;
+      bool masked = false;
+      if (p.causal && (t >> 1) == own) {
+        masked = true;
+        if (DKDV) lo = row_g - c0;               // query >= key
+        else hi = row_g - c0 + 1;                // key <= query
+      }
+      // per-column log-sum-exp / delta of the first 16 columns are requested before the wait
+      float lse2_c[16], dsc_c[16];
+      auto load_cols = [&](int off) {
+        const float4* l4 = reinterpret_cast<const float4*>(p.lse + bh + c0 + off);
+        const float4* d4 = reinterpret_cast<const float4*>(p.delta + bh + c0 + off);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 a = __ldg(l4 + q), d = __ldg(d4 + q);
+          lse2_c[4 * q] = a.x * LOG2E; lse2_c[4 * q + 1] = a.y * LOG2E;
+          lse2_c[4 * q + 2] = a.z * LOG2E; lse2_c[4 * q + 3] = a.w * LOG2E;
+          dsc_c[4 * q] = d.x * p.scale; dsc_c[4 * q + 1] = d.y * p.scale;
+          dsc_c[4 * q + 2] = d.z * p.scale; dsc_c[4 * q + 3] = d.w * p.scale;
+        }
+      };
+      if (DKDV) load_cols(0);
+      if (!mbar_wait_bounded_warp(smem_u32(s_full), it & 1, abort_flag, &g_attn_error, 75)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t s_addr = tmem_s + lane_base + hh * 32;
+      const uint32_t d_addr = tmem_dp + lane_base + hh * 32;
+      // two chunks of 16 columns; the packed bf16 results of chunk k go to columns [8 k, 8 k + 8)
+      // of this thread's own 32-column range, which holds fp32 values it has already read
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        uint32_t sv[16], dv[16], pp[8], dd[8];
+        tmem_ld_32x16(s_addr + 16 * k, sv);
+        tmem_ld_32x16(d_addr + 16 * k, dv);
+        if (DKDV && k == 1) load_cols(16);
+        tmem_ld_wait();
+        if (masked)
+          rebuild16<DKDV, true>(sv, dv, lse2_c, dsc_c, lse2_l, dsc_l, p.scale_log2, p.scale,
+                                lo - 16 * k, hi - 16 * k, pp, dd);
+        else
+          rebuild16<DKDV, false>(sv, dv, lse2_c, dsc_c, lse2_l, dsc_l, p.scale_log2, p.scale, 0, 16, pp, dd);
+        if (DKDV) tmem_st_32x8(s_addr + 8 * k, pp);
+        tmem_st_32x8(d_addr + 8 * k, dd);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(pds_full));
+    }
+    if (ok && n_it > 0 &&
+        mbar_wait_bounded_warp(smem_u32(acc_full), 0, abort_flag, &g_attn_error, 76)) {
+      tc_fence_after_sync();
+      const bool in_range = row_g < p.S;
+      __nv_bfloat16* d0p = in_range ? p.out0 + (long long)b * p.o0_sb + (long long)row_g * p.o0_ss +
+                                          (long long)h * p.o0_sh
+                                    : nullptr;
+      store_acc_row<D>(tmem_acc0 + lane_base, d0p, hh);
+      if (DKDV) {
+        __nv_bfloat16* d1p = in_range ? p.out1 + (long long)b * p.o1_sb + (long long)row_g * p.o1_ss +
+                                            (long long)h * p.o1_sh
+                                      : nullptr;
+        store_acc_row<D>(tmem_acc1 + lane_base, d1p, hh);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp_idx == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+template <int D, bool DKDV>
+cudaError_t launch_bwd2(const CUtensorMap& f0, const CUtensorMap& f1, const CUtensorMap& s0,
+                        const CUtensorMap& s1, const BwdParams& p, dim3 grid, cudaStream_t s) {
+  using L = Bwd2Smem<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd2_kernel<D, DKDV>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaError_t le = launch_pdl(flash_bwd2_kernel<D, DKDV>, grid, dim3(B2_THREADS), L::TOTAL, s, f0, f1, s0, s1, p);
+  if (le != cudaSuccess) return le;
+  g_attn_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+// LT_FLASH_BWD_V1=1 keeps the first-generation kernels (comparison runs)
+bool use_bwd_v1() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LT_FLASH_BWD_V1");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v != 0;
+}
+
 template <int D, bool DKDV>
 cudaError_t launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                        const CUtensorMap& tdo, const BwdParams& p, dim3 grid, cudaStream_t s) {
@@ -515,6 +842,33 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
                               (long long)g.do_sb, (long long)g.do_ss, (long long)g.do_sh);
   if (de != cudaSuccess) return de;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
+
+  if (a.D == 64 && a.S % BT == 0 && !use_bwd_v1() &&
+      ((reinterpret_cast<uintptr_t>(a.lse) | reinterpret_cast<uintptr_t>(g.delta)) & 15) == 0) {
+    // second-generation kernels: P / dS stay in tensor memory, two CTAs per SM
+    CUtensorMap q128, k128, v128, do128, q64, k64, v64, do64;
+    if (!attn_detail::make_qkv_map(&q128, a.q, a.D, a.S, a.H, a.B, a.q_ss, a.q_sh, a.q_sb, BT) ||
+        !attn_detail::make_qkv_map(&k128, a.k, a.D, a.S, a.H, a.B, a.k_ss, a.k_sh, a.k_sb, BT) ||
+        !attn_detail::make_qkv_map(&v128, a.v, a.D, a.S, a.H, a.B, a.v_ss, a.v_sh, a.v_sb, BT) ||
+        !attn_detail::make_qkv_map(&do128, g.d_o, a.D, a.S, a.H, a.B, g.do_ss, g.do_sh, g.do_sb, BT) ||
+        !attn_detail::make_qkv_map(&q64, a.q, a.D, a.S, a.H, a.B, a.q_ss, a.q_sh, a.q_sb, SUB) ||
+        !attn_detail::make_qkv_map(&k64, a.k, a.D, a.S, a.H, a.B, a.k_ss, a.k_sh, a.k_sb, SUB) ||
+        !attn_detail::make_qkv_map(&v64, a.v, a.D, a.S, a.H, a.B, a.v_ss, a.v_sh, a.v_sb, SUB) ||
+        !attn_detail::make_qkv_map(&do64, g.d_o, a.D, a.S, a.H, a.B, g.do_ss, g.do_sh, g.do_sb, SUB))
+      return cudaErrorInvalidValue;
+    BwdParams p2;
+    p2.S = a.S; p2.H = a.H; p2.causal = a.causal;
+    p2.scale = a.scale; p2.scale_log2 = a.scale * LOG2E;
+    p2.lse = a.lse; p2.delta = g.delta; p2.ds_out = nullptr;
+    dim3 grid2(a.S / BT, a.H, a.B);
+    p2.out0 = (__nv_bfloat16*)g.dk; p2.o0_sb = g.dk_sb; p2.o0_ss = g.dk_ss; p2.o0_sh = g.dk_sh;
+    p2.out1 = (__nv_bfloat16*)g.dv; p2.o1_sb = g.dv_sb; p2.o1_ss = g.dv_ss; p2.o1_sh = g.dv_sh;
+    cudaError_t e2 = launch_bwd2<64, true>(k128, v128, q64, do64, p2, grid2, stream);
+    if (e2 != cudaSuccess) return e2;
+    p2.out0 = (__nv_bfloat16*)g.dq; p2.o0_sb = g.dq_sb; p2.o0_ss = g.dq_ss; p2.o0_sh = g.dq_sh;
+    p2.out1 = nullptr; p2.o1_sb = p2.o1_ss = p2.o1_sh = 0;
+    return launch_bwd2<64, false>(q128, do128, k64, v64, p2, grid2, stream);
+  }
 
   CUtensorMap tq, tk, tv, tdo;
   if (!attn_detail::make_qkv_map(&tq, a.q, a.D, a.S, a.H, a.B, a.q_ss, a.q_sh, a.q_sb, BT) ||

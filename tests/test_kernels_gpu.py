@@ -434,6 +434,33 @@ def test_flash_attention(C, B, S, H, D, causal):
     assert torch.equal(packed[:, :, 0], dq) and torch.equal(packed[:, :, 2], dv)
 
 
+@pytest.mark.parametrize("B,S,H,D,sl", [(8, 1024, 12, 64, (slice(6, 8), slice(9, 12))),
+                                        (4, 2048, 16, 128, (slice(3, 4), slice(14, 16)))])
+def test_flash_attention_model_shapes(C, B, S, H, D, sl):
+    """The two benchmark shapes (8 and 16 key tiles: the K/V rings wrap many times, all heads
+    and batches launched); a slice of (batch, head) pairs is compared with fp32 attention."""
+    torch.manual_seed(14)
+    qkv = (torch.randn(B, S, 3, H, D, device="cuda") * 0.7).bfloat16()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    scale = 1.0 / math.sqrt(D)
+    o, lse = C.flash_forward(q, k, v, True, scale)
+    d_o = (torch.randn(B, S, H, D, device="cuda") * 0.5).bfloat16()
+    dq, dk, dv = C.flash_backward(q, k, v, o, lse, d_o, True, scale, None)
+    assert C.attention_device_error() == 0
+    bs, hs = sl
+    qf, kf, vf = (t[bs][:, :, hs].float().clone().requires_grad_(True) for t in (q, k, v))
+    ref_o, ref_lse = _attn_ref(qf, kf, vf, True, scale)
+    ref_o.backward(d_o[bs][:, :, hs].float())
+    torch.testing.assert_close(o[bs][:, :, hs].float(), ref_o.detach(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(lse[bs][:, hs], ref_lse.detach(), atol=2e-2, rtol=1e-3)
+    torch.testing.assert_close(dv[bs][:, :, hs].float(), vf.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(dk[bs][:, :, hs].float(), kf.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(dq[bs][:, :, hs].float(), qf.grad, atol=3e-2, rtol=3e-2)
+    # bitwise reproducible (no atomics anywhere in the backward)
+    dq2, dk2, dv2 = C.flash_backward(q, k, v, o, lse, d_o, True, scale, None)
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     # one GPU: a flag nobody sets makes the wait run out; the context stays usable
     import torch
