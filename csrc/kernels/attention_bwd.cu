@@ -20,6 +20,7 @@
 #include "gemm.h"
 
 #include <cuda.h>
+#include <stdio.h>
 #include <atomic>
 
 namespace lt {
@@ -231,11 +232,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int n_tiles = (p.S + BT - 1) / BT;
   // DKDV: this CTA owns key tile `own`, streams query tiles [first, n_tiles)
   // dQ  : this CTA owns query tile `own`, streams key tiles [0, last]
-  const int own = DKDV ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int own = DKDV ? (int)blockIdx.z : (int)gridDim.z - 1 - (int)blockIdx.z;
   const int it_begin = DKDV ? (p.causal ? own : 0) : 0;
   const int it_end = DKDV ? n_tiles : (p.causal ? own + 1 : n_tiles);
   const int n_it = it_end - it_begin;
@@ -509,7 +510,8 @@ struct Bwd2Smem {
   static constexpr int OFF_FIX0 = 0;
   static constexpr int OFF_FIX1 = FIX;
   static constexpr int OFF_STR = 2 * FIX;                 // [stage][2][STR]
-  static constexpr int OFF_BAR = OFF_STR + STAGES * 2 * STR;
+  static constexpr int OFF_SCAL = OFF_STR + STAGES * 2 * STR;   // [stage][2][64] floats: lse, delta
+  static constexpr int OFF_BAR = OFF_SCAL + STAGES * 2 * SUB * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
   static constexpr int TMEM_COLS = 128 + 2 * D <= 256 ? 256 : 512;
 };
@@ -564,9 +566,9 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int n_sub = p.S / SUB;
-  const int own = DKDV ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;  // longest first
+  const int own = DKDV ? (int)blockIdx.z : (int)gridDim.z - 1 - (int)blockIdx.z;  // longest first
   const int it_begin = DKDV ? (p.causal ? 2 * own : 0) : 0;
   const int it_end = DKDV ? n_sub : (p.causal ? 2 * own + 2 : n_sub);
   const int n_it = it_end - it_begin;
@@ -622,11 +624,19 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_cons
         if (!mbar_wait_bounded(smem_u32(&str_empty[st]), (use & 1) ^ 1, abort_flag, &g_attn_error, 71))
           break;
         const uint32_t sb = smem_u32(&str_full[st]);
-        mbar_arrive_expect_tx(sb, 2 * L::STR);
+        mbar_arrive_expect_tx(sb, 2 * L::STR + (DKDV ? 2 * SUB * 4 : 0));
 #pragma unroll
         for (int c = 0; c < DC; ++c) {
           tma_load_4d(smem_u32(str0(st) + c * SUB_CHUNK), &tm_str0, sb, 64 * c, t * SUB, h, b);
           tma_load_4d(smem_u32(str1(st) + c * SUB_CHUNK), &tm_str1, sb, 64 * c, t * SUB, h, b);
+        }
+        if (DKDV) {
+          // the 64 streamed queries' log-sum-exp and delta ride on the same barrier: every
+          // compute thread needs all of them, and reads them as shared-memory broadcasts
+          const long long row0 = ((long long)b * p.H + h) * p.S + (long long)t * SUB;
+          float* sc = reinterpret_cast<float*>(smem + L::OFF_SCAL) + st * 2 * SUB;
+          bulk_load(smem_u32(sc), p.lse + row0, SUB * 4, sb);
+          bulk_load(smem_u32(sc + SUB), p.delta + row0, SUB * 4, sb);
         }
       }
     }
@@ -711,22 +721,28 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_cons
         if (DKDV) lo = row_g - c0;               // query >= key
         else hi = row_g - c0 + 1;                // key <= query
       }
-      // per-column log-sum-exp / delta of the first 16 columns are requested before the wait
       float lse2_c[16], dsc_c[16];
-      auto load_cols = [&](int off) {
-        const float4* l4 = reinterpret_cast<const float4*>(p.lse + bh + c0 + off);
-        const float4* d4 = reinterpret_cast<const float4*>(p.delta + bh + c0 + off);
+      const float* sc = reinterpret_cast<const float*>(smem + L::OFF_SCAL) + (it % ST) * 2 * SUB + hh * 32;
+      auto load_cols = [&](int off) {   // broadcast reads: every lane takes the same 16 columns
+        const float4* l4 = reinterpret_cast<const float4*>(sc + off);
+        const float4* d4 = reinterpret_cast<const float4*>(sc + SUB + off);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float4 a = __ldg(l4 + q), d = __ldg(d4 + q);
+          const float4 a = l4[q], d = d4[q];
           lse2_c[4 * q] = a.x * LOG2E; lse2_c[4 * q + 1] = a.y * LOG2E;
           lse2_c[4 * q + 2] = a.z * LOG2E; lse2_c[4 * q + 3] = a.w * LOG2E;
           dsc_c[4 * q] = d.x * p.scale; dsc_c[4 * q + 1] = d.y * p.scale;
           dsc_c[4 * q + 2] = d.z * p.scale; dsc_c[4 * q + 3] = d.w * p.scale;
         }
       };
-      if (DKDV) load_cols(0);
       if (!mbar_wait_bounded_warp(smem_u32(s_full), it & 1, abort_flag, &g_attn_error, 75)) {
+        ok = false;
+        break;
+      }
+      // the stage's barrier completed long ago (the MMAs waited for it); observing it here
+      // makes the bulk-copied scalars visible to this thread
+      if (DKDV && !mbar_wait_bounded_warp(smem_u32(&str_full[it % ST]), (it / ST) & 1, abort_flag,
+                                          &g_attn_error, 77)) {
         ok = false;
         break;
       }
@@ -740,7 +756,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_cons
         uint32_t sv[16], dv[16], pp[8], dd[8];
         tmem_ld_32x16(s_addr + 16 * k, sv);
         tmem_ld_32x16(d_addr + 16 * k, dv);
-        if (DKDV && k == 1) load_cols(16);
+        if (DKDV) load_cols(16 * k);      // the stage (s_full follows str_full) is complete
         tmem_ld_wait();
         if (masked)
           rebuild16<DKDV, true>(sv, dv, lse2_c, dsc_c, lse2_l, dsc_l, p.scale_log2, p.scale,
@@ -860,7 +876,7 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
     p2.S = a.S; p2.H = a.H; p2.causal = a.causal;
     p2.scale = a.scale; p2.scale_log2 = a.scale * LOG2E;
     p2.lse = a.lse; p2.delta = g.delta; p2.ds_out = nullptr;
-    dim3 grid2(a.S / BT, a.H, a.B);
+    dim3 grid2(a.H, a.B, a.S / BT);   // tile index slowest: longest CTAs of every head go first
     p2.out0 = (__nv_bfloat16*)g.dk; p2.o0_sb = g.dk_sb; p2.o0_ss = g.dk_ss; p2.o0_sh = g.dk_sh;
     p2.out1 = (__nv_bfloat16*)g.dv; p2.o1_sb = g.dv_sb; p2.o1_ss = g.dv_ss; p2.o1_sh = g.dv_sh;
     cudaError_t e2 = launch_bwd2<64, true>(k128, v128, q64, do64, p2, grid2, stream);
@@ -881,7 +897,7 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
   p.S = a.S; p.H = a.H; p.causal = a.causal;
   p.scale = a.scale; p.scale_log2 = a.scale * LOG2E;
   p.lse = a.lse; p.delta = g.delta;
-  dim3 grid((a.S + BT - 1) / BT, a.H, a.B);
+  dim3 grid(a.H, a.B, (a.S + BT - 1) / BT);
 
   p.out0 = (__nv_bfloat16*)g.dk; p.o0_sb = g.dk_sb; p.o0_ss = g.dk_ss; p.o0_sh = g.dk_sh;
   p.out1 = (__nv_bfloat16*)g.dv; p.o1_sb = g.dv_sb; p.o1_ss = g.dv_ss; p.o1_sh = g.dv_sh;

@@ -195,8 +195,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // longest (most key tiles) query tiles first
-  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int q_tile = (int)gridDim.z - 1 - (int)blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int q0 = q_tile * BM;
   const int n_kv_all = (p.S + BN - 1) / BN;
   const int n_kv = p.causal ? (q_tile + 1 < n_kv_all ? q_tile + 1 : n_kv_all) : n_kv_all;
@@ -590,8 +590,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp_idx = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // longest tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int q_tile = (int)gridDim.z - 1 - (int)blockIdx.z;   // longest tiles first, over the WHOLE grid
+  const int h = blockIdx.x, b = blockIdx.y;
   const int q0 = q_tile * BM;
   const int n_kv_all = (p.S + BN - 1) / BN;
   const int n_kv = p.causal ? (q_tile + 1 < n_kv_all ? q_tile + 1 : n_kv_all) : n_kv_all;
@@ -882,7 +882,7 @@ cudaError_t launch_fwd_v2(const AttnArgs& a, cudaStream_t stream) {
   p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
   p.lse = a.lse;
   p.tmem_p = use_tmem_p() ? 1 : 0;
-  dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
+  dim3 grid(a.H, a.B, (a.S + BM - 1) / BM);   // tile index slowest: the hardware hands out the longest tiles of every head first
   cudaError_t le = launch_pdl(flash_fwd2_kernel<D>, grid, dim3(V2_THREADS), L::TOTAL, stream, tq, tk, tv, p);
   if (le != cudaSuccess) return le;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
@@ -922,7 +922,7 @@ cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.o_sb = a.o_sb; p.o_ss = a.o_ss; p.o_sh = a.o_sh;
   p.lse = a.lse;
   p.tmem_p = 0;
-  dim3 grid((a.S + BM - 1) / BM, a.H, a.B);
+  dim3 grid(a.H, a.B, (a.S + BM - 1) / BM);   // tile index slowest: the hardware hands out the longest tiles of every head first
   cudaError_t le = launch_pdl(flash_fwd_kernel<D>, grid, dim3(NUM_THREADS), L::TOTAL, stream, tq, tk, tv, p);
   if (le != cudaSuccess) return le;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);

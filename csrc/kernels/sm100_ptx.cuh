@@ -115,6 +115,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16),
+// its bytes credited to `bar`.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
 // ----------------------------------------------------------------------------
 // tcgen05: TMEM allocation, MMA, commit, loads, fences
 // ----------------------------------------------------------------------------
