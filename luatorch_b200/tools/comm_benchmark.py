@@ -25,7 +25,36 @@ import torch
 import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-NVLINK_BPS = 770e9
+NVLINK_NOMINAL_BPS = 900e9     # NVLink 5: per direction per GPU
+
+
+def measure_peer_copy(buf, rank, world, nbytes=256 << 20, iters=10):
+    """Bytes per second one GPU pulls from ONE peer with this package's copy kernel (every rank
+    reads its right-hand neighbour at the same time): the measured link rate the rooflines
+    below are quoted against, next to the nominal 900 GB/s."""
+    from luatorch_b200 import _backend as B
+    from luatorch_b200.distributed import comm
+    C = B.ext()
+    nbytes = min(nbytes, buf.nbytes)
+    status = comm.status_buffer()
+    best = 0.0
+    for root in range(min(world, 2)):
+        def fn():
+            C.peer_broadcast(buf.ptrs, buf.signal_ptrs, rank, world, root, 0, nbytes, 0, status)
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        best = max(best, nbytes / (float(t.item()) * 1e-3))
+    return best
 
 
 def main():
@@ -52,6 +81,8 @@ def main():
     seg_wd = torch.tensor([0.1], device="cuda")
     status = comm.status_buffer()
     blocks = int(os.environ.get("LT_COMM_BLOCKS", "0"))   # 0 = the kernel's default
+    grad_mc = grad_buf.multicast_ptr + comm.SIGNAL_PAD_BYTES if grad_buf.multicast_ptr else 0
+    shadow_mc = shadow_buf.multicast_ptr + comm.SIGNAL_PAD_BYTES if shadow_buf.multicast_ptr else 0
 
     def timed(fn, iters=10, warmup=3):
         for _ in range(warmup):
@@ -68,16 +99,22 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # with every rank reading from one root, the root's outgoing link carries world - 1 streams:
+    # a reader's share is the per-direction link rate divided by the readers
+    copy_bps = measure_peer_copy(grad_buf, rank, world) * max(1, world - 1)
+    NVLINK_BPS = copy_bps
     if rank == 0:
-        print("world %d; NVLink bound %.0f GB/s per direction per GPU; HBM %.0f GB/s" % (world, NVLINK_BPS / 1e9, hbm / 1e9))
+        print("world %d; peer copy measured %.0f GB/s out of one GPU (nominal %.0f); HBM %.0f GB/s; multicast %s"
+              % (world, copy_bps / 1e9, NVLINK_NOMINAL_BPS / 1e9, hbm / 1e9, "yes" if grad_mc else "no"))
     for mb in sizes_mb:
         n = mb * 1024 * 1024 // 2 // (8 * world) * (8 * world)
         nbytes = n * 2
 
-        def fused(mode):
+        def fused(mode, nvls=False):
             C.allreduce_adamw(grad_buf.ptrs, grad_buf.signal_ptrs, rank, world, 0, n, master, shadow_buf.ptrs, m, v,
-                              seg_end, seg_wd, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.05, 1.0 / world, comm.next_epoch(), mode,
-                              blocks, status)
+                              seg_end, seg_wd, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.05, 1.0 / world, 0, mode,
+                              blocks, status, -1, 0, 0.0, False, grad_mc if nvls else 0,
+                              shadow_mc if nvls else 0, None, None)
 
         def nccl_path():
             g = grad[:n]
@@ -86,20 +123,29 @@ def main():
                          1.0 / world, None)
 
         rows = []
-        for name, fn, link_bytes, hbm_bytes in [
+        cases = [
             # bytes ENTERING a GPU over NVLink: a two-shot all-reduce brings in (W-1)/W of the
             # bucket as read responses of the reduce-scatter and another (W-1)/W as the peers'
             # all-gather stores; the one-shot form reads the whole bucket from every peer
             ("fused-sharded", lambda: fused(1), 2.0 * nbytes * (world - 1) / world, n / world * 26.0 + nbytes / world * 2),
             ("fused-replicated", lambda: fused(0), nbytes * (world - 1), n * 26.0 + nbytes),
             ("nccl + adamw", nccl_path, 2.0 * nbytes * (world - 1) / world, n * 28.0),
-        ]:
+        ]
+        if grad_mc:
+            # in-switch reduction: a GPU receives its reduced slice once and every peer's
+            # published slice once, and sends each of its gradient bytes once
+            cases.insert(1, ("fused-sharded-nvls", lambda: fused(1, True), 1.0 * nbytes,
+                             n / world * 26.0 + nbytes / world * 2))
+        for name, fn, link_bytes, hbm_bytes in cases:
             ms = timed(fn)
             bound_s = max(link_bytes / NVLINK_BPS, hbm_bytes / hbm)
-            rows.append((name, ms, bound_s * 1e3 / ms if ms > 0 else 0.0))
+            bound_n = max(link_bytes / NVLINK_NOMINAL_BPS, hbm_bytes / hbm)
+            rows.append((name, ms, bound_s * 1e3 / ms if ms > 0 else 0.0, bound_n * 1e3 / ms if ms > 0 else 0.0))
         comm.check_status()
         if rank == 0:
-            print("bucket %4d MB (bf16 grads): " % mb + "  ".join("%s %.3f ms (%.0f%% of roofline)" % (a, b, 100 * c) for a, b, c in rows), flush=True)
+            print("bucket %4d MB (bf16 grads): " % mb + "  ".join(
+                "%s %.3f ms (%.0f%% of measured-link roofline, %.0f%% of 900 GB/s)" % (a, b, 100 * c, 100 * d)
+                for a, b, c, d in rows), flush=True)
     # ---- all-gather fused into the consuming GEMM
     peak = 1.59e15
     if os.path.exists(p):
