@@ -330,7 +330,8 @@ void softmax_scores_backward(const Tensor& p, Tensor& dp, int64_t rows_per_batch
                                     (float)scale, causal, rows_per_batch, cur_stream()),
         "softmax_scores_backward");
 }
-// logits [rows, ld] with `cols` valid columns -> (loss[1] fp32, lse[rows] fp32, err_flag[1] int)
+// logits [rows, ld] with `cols` valid columns -> (loss[1] fp32, lse[rows] fp32, err[4] int:
+// flag, row, offending label of the first out-of-range label seen)
 std::vector<Tensor> cross_entropy_forward(const Tensor& logits, int64_t cols, const Tensor& labels) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
   need_cuda_contig(labels, "labels");
@@ -338,7 +339,7 @@ std::vector<Tensor> cross_entropy_forward(const Tensor& logits, int64_t cols, co
   const int64_t rows = logits.size(0);
   auto fo = logits.options().dtype(at::kFloat);
   Tensor lse = at::empty({rows}, fo), row_loss = at::empty({rows}, fo), loss = at::empty({1}, fo);
-  Tensor err = at::zeros({1}, logits.options().dtype(at::kInt));
+  Tensor err = at::zeros({4}, logits.options().dtype(at::kInt));
   check(lt::cross_entropy_forward(dt(logits), logits.data_ptr(), logits.stride(0),
                                   labels.data_ptr(), label_kind(labels), rows, cols,
                                   lse.data_ptr<float>(), row_loss.data_ptr<float>(),
@@ -356,7 +357,7 @@ std::vector<Tensor> cross_entropy_fused(Tensor& logits, int64_t cols, const Tens
   const int64_t rows = logits.size(0);
   auto fo = logits.options().dtype(at::kFloat);
   Tensor lse = at::empty({rows}, fo), row_loss = at::empty({rows}, fo), loss = at::empty({1}, fo);
-  Tensor err = at::zeros({1}, logits.options().dtype(at::kInt));
+  Tensor err = at::zeros({4}, logits.options().dtype(at::kInt));
   check(lt::cross_entropy_fused(dt(logits), logits.data_ptr(), logits.stride(0), labels.data_ptr(),
                                 label_kind(labels), rows, cols, lse.data_ptr<float>(),
                                 row_loss.data_ptr<float>(), err.data_ptr<int>(), (float)grad_scale,
@@ -483,7 +484,7 @@ std::vector<Tensor> embedding_forward(const Tensor& table, const Tensor& ids, co
   c10::cuda::CUDAGuard guard(table.device());
   const int64_t n = ids.numel(), dim = table.size(1), vocab = table.size(0);
   Tensor out = at::empty({n, dim}, table.options());
-  Tensor err = at::zeros({1}, table.options().dtype(at::kInt));
+  Tensor err = at::zeros({4}, table.options().dtype(at::kInt));
   check(lt::embedding_forward(dt(table), table.data_ptr(), ids.data_ptr(), label_kind(ids),
                               optptr(pos_table), seq_len > 0 ? seq_len : 1, out.data_ptr(), n, dim,
                               vocab, err.data_ptr<int>(), cur_stream()), "embedding_forward");

@@ -30,7 +30,11 @@ embedding_fwd_kernel(const T* __restrict__ table, const void* __restrict__ ids, 
   if (t >= n_tokens) return;
   int64_t id = read_id(ids, id_kind, t);
   if (id < 0 || id >= vocab) {
-    if (lane == 0 && err_flag) atomicOr(err_flag, 1);
+    // status word, never a trap: [0] flag, [1] token position, [2] offending id (first seen)
+    if (lane == 0 && err_flag && atomicOr(err_flag, 1) == 0) {
+      err_flag[1] = (int)t;
+      err_flag[2] = (int)id;
+    }
     id = 0;
   }
   const T* src = table + id * dim;

@@ -162,7 +162,8 @@ ce_forward_kernel(const T* __restrict__ logits, int64_t ld, const void* __restri
     lse[r] = l;
     const int64_t lab = read_label(labels, label_kind, r);
     if (lab < 0 || lab >= cols) {
-      if (err_flag) atomicOr(err_flag, 1);
+      // status word, never a trap: [0] flag, [1] row, [2] offending label (first seen)
+      if (err_flag && atomicOr(err_flag, 1) == 0) { err_flag[1] = (int)r; err_flag[2] = (int)lab; }
       row_loss[r] = 0.0f;
     } else {
       row_loss[r] = l - VecIO<T>::ld(row + lab);
@@ -230,7 +231,7 @@ ce_fused_kernel(T* logits, int64_t ld, const void* __restrict__ labels, int labe
   if (threadIdx.x == 0) {
     lse[r] = l;
     if (bad) {
-      if (err_flag) atomicOr(err_flag, 1);
+      if (err_flag && atomicOr(err_flag, 1) == 0) { err_flag[1] = (int)r; err_flag[2] = (int)lab; }
       row_loss[r] = 0.0f;
     } else {
       row_loss[r] = l - VecIO<T>::ld(row + lab);

@@ -15,6 +15,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from .utils import debug as _debug
+
 _C = None
 _C_error: Optional[BaseException] = None
 
@@ -379,6 +381,8 @@ def gemm(a, b, *, a_t=False, b_t=False, out=None, out_dtype=None, alpha=1.0, acc
            1, 1, 0, 0, 0, 0, 0, 0, float(alpha), bool(accumulate), bias, int(act), residual,
            residual.stride(0) if residual is not None else 0, aux_out, aux_in,
            aux_in.stride(0) if aux_in is not None else 0, 0)
+    if _debug._on:
+        _debug.check_kernels(C)
     return out
 
 
@@ -764,6 +768,8 @@ def attention_forward(q, k, v, causal: bool, scale: float):
             q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
         if D in (64, 128):
             o, lse = ext().flash_forward(q, k, v, causal, scale)
+            if _debug._on:
+                _debug.check_kernels(ext())
             return o, ("flash", lse)
         o, p = _attn_composed_forward(q, k, v, causal, scale)
         return o, ("composed", p)
@@ -800,7 +806,10 @@ def attention_backward(q, k, v, o, ctx, d_o, causal: bool, scale: float, packed_
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
     if kind == "flash":
-        return ext().flash_backward(q, k, v, o, saved, d_o, causal, scale, packed_out)
+        grads = ext().flash_backward(q, k, v, o, saved, d_o, causal, scale, packed_out)
+        if _debug._on:
+            _debug.check_kernels(ext())
+        return grads
     Bn, S, H, D = q.shape
     if packed_out is not None:
         dq, dk, dv = packed_out[:, :, 0], packed_out[:, :, 1], packed_out[:, :, 2]

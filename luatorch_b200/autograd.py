@@ -128,6 +128,12 @@ def _leaf_done(node: Node) -> None:
 
 
 def backward(loss: Tensor, grad: Optional[Tensor] = None) -> None:
+    from .utils import nvtx
+    with nvtx.range("autograd.backward"):
+        _backward(loss, grad)
+
+
+def _backward(loss: Tensor, grad: Optional[Tensor] = None) -> None:
     if grad is None:
         seed = torch.ones_like(loss._t)
     else:

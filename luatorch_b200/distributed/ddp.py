@@ -52,6 +52,7 @@ import os
 from ..parallel.arena import ParamArena, StateShards, bucket_align_for
 from ..tensor import Tensor
 from . import comm
+from ..utils import nvtx
 
 SMALL_MODEL_BYTES = 4 << 20    # "auto": below this one one-shot launch beats the two-shot form
 
@@ -148,7 +149,8 @@ class DDP:
 
     # ------------------------------------------------------------------ reference surface
     def forward(self, *args, **kwargs):
-        return self.model.forward(*args, **kwargs)
+        with nvtx.range("ddp.forward"):
+            return self.model.forward(*args, **kwargs)
 
     __call__ = forward
 
@@ -289,6 +291,7 @@ class DDP:
         ev.record(cur)
         self._comm_stream.wait_event(ev)
         self._comm_used = True
+        nvtx.push("ddp.bucket%d.reduce+optimizer" % bi)
         with torch.cuda.stream(self._comm_stream):
             if self._profile:
                 e0 = torch.cuda.Event(enable_timing=True)
@@ -348,6 +351,7 @@ class DDP:
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
                 self._bucket_events.append((bi, e0, e1))
+        nvtx.pop()
 
     def _bucket_segments(self, bi: int, seg_end: torch.Tensor) -> torch.Tensor:
         """Weight-decay segment ends in the bucket's own coordinates (built once per bucket)."""
@@ -363,6 +367,7 @@ class DDP:
         """Make sure every bucket has been issued and the compute stream waits for them."""
         if self._synced or self._accumulate:
             return
+        nvtx.push("ddp.sync_gradients")
         self._launch_ready(force=True)
         # join the communication stream only if this step forked onto it (a stream that did no
         # work must not be waited on from a stream that is being captured into a graph)
@@ -370,6 +375,7 @@ class DDP:
             ev = torch.cuda.Event()
             ev.record(self._comm_stream)
             torch.cuda.current_stream().wait_event(ev)
+        nvtx.pop()
         self._synced = True
 
     def _optimizer_step(self) -> None:

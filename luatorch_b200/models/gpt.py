@@ -21,6 +21,7 @@ from typing import List, Optional
 import torch
 
 from .. import _backend as B
+from ..utils import debug as _debug
 from .. import autograd
 from ..nn.dropout import Dropout
 from ..nn.embedding import Embedding, embedding_backward_into
@@ -67,6 +68,7 @@ class GPT(Module):
             else:
                 pos_table = self.pos_enc._table(table)
             y, err = B.ext().embedding_forward(table, ids, pos_table, seq_len)
+            _debug.check_index_word(err, "GPT token embedding: token id")
             out = Tensor(_data=y)
             batch = ids.numel() // seq_len
             pos_enc = self.pos_enc

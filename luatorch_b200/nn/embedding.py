@@ -11,6 +11,7 @@ import sys
 import torch
 
 from .. import _backend as B
+from ..utils import debug as _debug
 from .. import autograd
 from ..tensor import Tensor
 from .module import Module, param
@@ -43,6 +44,7 @@ class Embedding(Module):
                 ids = ids.cuda()
             table = w._compute if w._compute is not None else w._t
             y, err = B.ext().embedding_forward(table, B._labels(ids), None, 1)
+            _debug.check_index_word(err, "Embedding: token id")
             out = Tensor(_data=y)
         else:
             idx = ids.long()

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 
 from .. import _backend as B
+from ..utils import debug as _debug
 from .. import autograd
 from ..tensor import Tensor
 from .module import Module
@@ -75,6 +76,7 @@ class CrossEntropyLoss(Module):
             else:
                 loss, lse, err = B.cross_entropy_device(logits, labels, cols)
             self.last_error_flag = err
+            _debug.check_index_word(err, "CrossEntropyLoss: label")
         else:
             r = B.cross_entropy_full(logits, labels, cols)
             if r is None:

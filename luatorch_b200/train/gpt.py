@@ -127,6 +127,8 @@ def main(argv=None):
     window = 0
     for step in range(first_step, cfg.get("max_steps") + 1):
         x, y = batch()
+        if runner is None and cuda and (step % cfg.get("print_every")) == 0:
+            ddp.profile_next_step(True)      # time this step's bucket kernels for the log line
         loss = runner(x, y) if runner is not None else one_step(x, y)
         lr = sched.step()
         window += 1
@@ -134,7 +136,12 @@ def main(argv=None):
             ms = timer.elapsed_ms()
             if rank == 0:
                 logger.step = step - 1
+                if runner is None and cuda:
+                    logger.log_comm(ddp.comm_profile(),
+                                    {"allocated_mb": round(lf.Tensor.cuda_memory_allocated() / 1e6, 1),
+                                     "cached_mb": round(lf.Tensor.cuda_memory_cached() / 1e6, 1)})
                 logger.log(loss.item(), None, lr, tokens=Bm * S * world * window, step_ms=ms)
+            ddp.profile_next_step(False)
             ddp.check()
             timer.reset()
             window = 0

@@ -2,5 +2,7 @@
 from .config import Config
 from .logger import Logger
 from .timing import ClockSampler, DeviceTimer
+from . import nvtx
+from . import debug
 
-__all__ = ["Logger", "Config", "DeviceTimer", "ClockSampler"]
+__all__ = ["Logger", "Config", "DeviceTimer", "ClockSampler", "nvtx", "debug"]

@@ -1,7 +1,8 @@
 """Training logger (lua/luatorch/utils/logger.lua): running means of loss / accuracy,
 a line every `print_every` steps, full history, CSV export with the header
 `step,epoch,loss,accuracy,lr`.  Extensions: optional tokens-per-second column fed with
-device-timed step durations, and a JSON-lines sink."""
+device-timed step durations, per-bucket communication time and its overlap with backward
+(`log_comm`, fed from `DDP.comm_profile()`), memory-pool statistics, and a JSON-lines sink."""
 from __future__ import annotations
 
 import json
@@ -46,6 +47,20 @@ class Logger:
         if self.step % self.print_every == 0:
             self.print_summary()
 
+    def log_comm(self, profile: dict, pool: Optional[dict] = None) -> None:
+        """Record the data-parallel engine's communication profile (`DDP.comm_profile()`:
+        device time of every bucket's fused reduce + optimizer kernel, their sum, and the share
+        that ran under backward) and optional allocator statistics; printed with the next
+        summary line and written to the JSON-lines sink."""
+        self.comm = {"buckets_ms": [round(x, 4) for x in profile.get("buckets_ms", [])],
+                     "total_ms": round(profile.get("total_ms", 0.0), 4),
+                     "overlap": round(profile.get("overlap", 0.0), 4)}
+        if pool:
+            self.comm["pool"] = pool
+        if self._jsonl is not None:
+            self._jsonl.write(json.dumps({"step": self.step, "comm": self.comm}) + "\n")
+            self._jsonl.flush()
+
     def set_epoch(self, epoch: int):
         self.epoch = epoch
 
@@ -64,6 +79,10 @@ class Logger:
             parts.append("lr %.2e" % self.current_lr)
         if self.running_ms > 0 and self.running_tokens > 0:
             parts.append("tok/s %.0f" % (self.running_tokens / (self.running_ms * 1e-3)))
+        comm = getattr(self, "comm", None)
+        if comm and comm["buckets_ms"]:
+            parts.append("comm %.3f ms in %d buckets (%.0f%% under backward)" % (
+                comm["total_ms"], len(comm["buckets_ms"]), 100 * comm["overlap"]))
         print("  ".join(parts))
         self.running_loss = self.running_acc = 0.0
         self.running_n = 0

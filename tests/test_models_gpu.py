@@ -180,3 +180,41 @@ def test_tensor_front_end_on_gpu():
     T.sync()
     assert T.has_inf_nan(a) is False
     assert T.cuda_memory_allocated() > 0
+
+
+def test_debug_mode_names_the_offending_token_and_label():
+    """Debug mode reads the kernels' status words after each call: a token id or a label
+    outside its range raises with the position and the value (the kernels themselves never
+    trap: they record the fact and carry on with a safe value)."""
+    dbg = lf.utils.debug
+    vocab, embed, heads, layers, seq, batch = 64, 64, 1, 1, 128, 1
+    lf.manual_seed(3)
+    model = lf.models.GPT(vocab, embed, heads, layers, seq, 0.0, pos="learned")
+    lf.cuda.amp.autocast_bf16(model)
+    crit = nn.CrossEntropyLoss(vocab)
+    tok = torch.randint(0, vocab, (batch, seq))
+    good_x = T.wrap(tok.float().cuda())
+    lab = torch.randint(0, vocab, (batch * seq,)).float()
+    dbg.enable(True)
+    try:
+        before = dbg.checked
+        ag.zero_graph()
+        loss = crit(model(good_x), T.wrap(lab.cuda()))
+        ag.backward(loss)
+        assert dbg.checked > before + 4          # embedding, GEMMs, attention, loss were all checked
+        bad = tok.clone().float()
+        bad[0, 5] = vocab + 7
+        with pytest.raises(IndexError, match="position 5 holds %d" % (vocab + 7)):
+            ag.zero_graph()
+            model(T.wrap(bad.cuda()))
+        bad_lab = lab.clone()
+        bad_lab[9] = -3
+        with pytest.raises(IndexError, match="position 9 holds -3"):
+            ag.zero_graph()
+            crit(model(good_x), T.wrap(bad_lab.cuda()))
+    finally:
+        dbg.enable(False)
+    # outside debug mode the same inputs do not raise and the context stays healthy
+    ag.zero_graph()
+    out = model(T.wrap(bad.cuda()))
+    assert torch.isfinite(out._t.float()).all()

@@ -272,3 +272,32 @@ def test_reference_constructor_spelling():
     for cls in (lf.optim.WarmupScheduler, lf.data.DataLoader, lf.distributed.DDP, lf.utils.Logger,
                 lf.utils.Config, lf.cuda.GradScaler, lf.models.GPT, lf.models.MLP, lf.nn.Linear):
         assert callable(getattr(cls, "new"))
+
+
+def test_nvtx_ranges_and_comm_fields_in_the_logger(tmp_path, capsys):
+    import json
+    import torch
+    import luatorch_b200 as lf
+    nvtx = lf.utils.nvtx
+    before = nvtx.pushed
+    with nvtx.range("off"):
+        pass
+    assert nvtx.pushed == before                      # off by default: nothing is opened
+    nvtx.enable(True)
+    try:
+        m = lf.nn.Sequential(lf.nn.Linear(4, 4))
+        x, y = lf.Tensor.wrap(torch.randn(2, 4)), lf.Tensor.wrap(torch.randn(2, 4))
+        lf.autograd.zero_graph()
+        lf.autograd.backward(lf.nn.MSELoss()(m(x), y))
+        assert nvtx.pushed == before + 1              # the backward pass is one range
+    finally:
+        nvtx.enable(False)
+    path = str(tmp_path / "log.jsonl")
+    lg = lf.utils.Logger(1, jsonl_path=path)
+    lg.log_comm({"buckets_ms": [0.1, 0.25], "total_ms": 0.35, "overlap": 0.2857}, {"allocated_mb": 12.0})
+    lg.log(1.5, None, 1e-3, tokens=100, step_ms=2.0)
+    out = capsys.readouterr().out
+    assert "comm 0.350 ms in 2 buckets (29% under backward)" in out and "tok/s 50000" in out
+    recs = [json.loads(l) for l in open(path)]
+    assert recs[0]["comm"]["buckets_ms"] == [0.1, 0.25] and recs[0]["comm"]["pool"]["allocated_mb"] == 12.0
+    assert recs[1]["tokens_per_s"] == 50000.0
