@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--mode", default="sharded", choices=["sharded", "replicated", "nccl"])
     ap.add_argument("--bucket-mb", type=float, default=32.0)
     ap.add_argument("--micro-batch", type=int, default=0)
+    ap.add_argument("--graph", type=int, default=int(os.environ.get("LT_BENCH_GRAPH", "0")),
+                    help="1: replay the whole step as a CUDA graph on every rank (lf.cuda.GraphedStep)")
     return ap.parse_args()
 
 
@@ -95,16 +97,30 @@ def run_ours(args):
         opt.step()
         return loss
 
+    runner = None
+    kernels_per_replay = 0
+    if args.graph:
+        # the public whole-step replay: static input tensors, one graph launch per step
+        gx = lf.Tensor.wrap(dev_batches[0][0]._t.clone())
+        gy = lf.Tensor.wrap(dev_batches[0][1]._t.clone())
+        c_before = sum(lf.launch_counts())
+        runner = lf.cuda.GraphedStep(lambda: train_step(gx, gy), opt, inputs=(gx, gy), warmup=2,
+                                     pdl=True)
+        # two eager warm-up steps and the capture each went through the launchers once: a
+        # third of the difference is the number of this package's kernels inside the graph
+        kernels_per_replay = (sum(lf.launch_counts()) - c_before) // 3
+
     def step_resident(i):
         x, y = dev_batches[i % n_pool]
-        return train_step(x, y)
+        return runner(x, y) if runner is not None else train_step(x, y)
 
     def step_e2e(i):
         t = host_tokens[i % n_pool]
         d = t.to("cuda", non_blocking=True)          # H2D from pinned memory, every step
         x = lf.Tensor.wrap(d[:, :-1].contiguous())
         y = lf.Tensor.wrap(d[:, 1:].contiguous().reshape(-1))
-        return train_step(x, y).item()                # D2H read of the loss, every step
+        loss = runner(x, y) if runner is not None else train_step(x, y)
+        return loss.item()                            # D2H read of the loss, every step
 
     def sync_all():
         torch.cuda.synchronize()
@@ -154,11 +170,12 @@ def run_ours(args):
             "config": bench_config(args.config, model.num_params(), B, S, world),
             "engine": {"params": model.num_params(), "dp_mode": ddp.mode, "nvls": bool(ddp.nvls),
                        "state_sharded": ddp.arena.state_shards is not None,
-                       "buckets": len(ddp.buckets)},
+                       "buckets": len(ddp.buckets), "cuda_graph": bool(args.graph)},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 4, "d2h_bytes_per_step": 4,
                     "final_loss": loss_val},
-            "gpu_launches": int(launches),
+            # host launches counted in the timed region, plus the kernels each graph replay runs
+            "gpu_launches": int(launches + kernels_per_replay * args.steps),
             "clocks": clocks,
         }
         print(json.dumps(out), flush=True)
