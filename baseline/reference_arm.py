@@ -44,7 +44,7 @@ TP = C.POINTER(RefTensor)
 def _load():
     lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
     unary = ["tensor_transpose_cuda", "tensor_softmax_cuda", "tensor_add_broadcast_backward_cuda",
-             "tensor_to_cuda", "tensor_tanh_cuda"]
+             "tensor_to_cuda", "tensor_tanh_cuda", "tensor_copy"]
     binary = ["tensor_matmul_cuda", "tensor_bmm_cuda", "tensor_add_cuda", "tensor_mul_cuda",
               "tensor_sub_cuda", "tensor_add_broadcast_cuda", "tensor_fused_gelu_bias_cuda",
               "tensor_cross_entropy_loss_cuda", "tensor_cross_entropy_loss_backward_cuda"]

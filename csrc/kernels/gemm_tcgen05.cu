@@ -1297,6 +1297,16 @@ int choose_split(const GemmArgs& a, TileChoice* slice_tile) {
   if (batch != 1 || a.bias || a.act != GEMM_ACT_NONE || a.residual || a.aux_out || a.aux_in ||
       a.causal_tiles || a.causal_k || a.K < 2048 || getenv("LT_GEMM_NO_SPLIT"))
     return 1;
+  // LT_GEMM_SPLIT=n forces a split factor (tuning aid): the slice tile still comes from the model
+  static int forced_split = -1;
+  if (forced_split < 0) {
+    const char* e = getenv("LT_GEMM_SPLIT");
+    forced_split = e ? atoi(e) : 0;
+  }
+  if (forced_split > 1 && a.K % (forced_split * BK) == 0) {
+    *slice_tile = choose_tile(a, a.K / forced_split, forced_split, true);
+    return forced_split;
+  }
   int best_s = 1;
   double best_cost = whole.cost;
   const int splits[11] = {2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};

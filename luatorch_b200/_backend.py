@@ -484,7 +484,7 @@ def cross_entropy_full(logits: torch.Tensor, labels: torch.Tensor, n_classes: Op
     if logits.is_cuda:
         lg = logits if logits.stride(-1) == 1 else logits.contiguous()
         loss, lse, err = ext().cross_entropy_forward(lg, cols, _labels(labels))
-        if int(err.item()) != 0:
+        if int(err[0].item()) != 0:
             return None
         return loss, lse
     lab = labels.reshape(-1).long()
