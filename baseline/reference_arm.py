@@ -371,6 +371,14 @@ def run(args, cfg):
     cfg = dict(cfg)
     if getattr(args, "micro_batch", 0):
         cfg["micro_batch"] = args.micro_batch
+    pg = None
+    if world > 1:
+        # Host-side rendezvous only (barrier + max of the per-rank times).  It is imported
+        # BEFORE the reference library: that library pulls in the system libnccl, and the
+        # process-group package needs its own, newer one to be the first loaded.
+        import torch.distributed as dist
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        pg = dist
     try:
         rt = C.CDLL("libcudart.so.12")
     except OSError:
@@ -391,11 +399,6 @@ def run(args, cfg):
     import random
     rng = random.Random(1234 + rank)
     tokens = [rng.randrange(cfg["vocab"]) for _ in range(cfg["micro_batch"] * cfg["seq"])]
-    pg = None
-    if world > 1:
-        import torch.distributed as dist   # host-side rendezvous only: barrier + max of the times
-        dist.init_process_group("gloo", rank=rank, world_size=world)
-        pg = dist
     try:
         rep = Replica(lib, rt, dev, cfg, tokens)
     except RuntimeError as e:

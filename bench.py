@@ -11,8 +11,10 @@ dropout 0), learned positions, seq 1024, micro-batch 8 per GPU, next-token cross
 AdamW lr 6e-4 wd 0.1, bf16 compute with fp32 master weights; synthetic uniform tokens,
 random-init weights.  Weak scaling: per-GPU work is fixed.
 
-Two timed regions of K steps each, both bracketed by barrier + synchronize and timed with CUDA
-events on the launching stream:
+The step runs through the public API; by default it is captured once into a CUDA graph
+(`lf.cuda.GraphedStep`: forward, loss, backward, the per-bucket fused reduce + AdamW kernels) and
+replayed, `--graph 0` launches it eagerly.  Two timed regions of K steps each, both bracketed
+by barrier + synchronize and timed with CUDA events on the launching stream:
   value      steps fed from device-resident token batches (kernel-side throughput)
   e2e.value  steps through the same public API with every step's tokens copied from pinned
              host memory and the loss read back to the host
@@ -48,8 +50,9 @@ def parse_args():
     ap.add_argument("--mode", default="sharded", choices=["sharded", "replicated", "nccl"])
     ap.add_argument("--bucket-mb", type=float, default=32.0)
     ap.add_argument("--micro-batch", type=int, default=0)
-    ap.add_argument("--graph", type=int, default=int(os.environ.get("LT_BENCH_GRAPH", "0")),
-                    help="1: replay the whole step as a CUDA graph on every rank (lf.cuda.GraphedStep)")
+    ap.add_argument("--graph", type=int, default=int(os.environ.get("LT_BENCH_GRAPH", "1")),
+                    help="1 (default): replay the whole step as a CUDA graph on every rank "
+                         "(lf.cuda.GraphedStep); 0: eager launches with programmatic dependent launch")
     return ap.parse_args()
 
 
@@ -104,11 +107,20 @@ def run_ours(args):
         gx = lf.Tensor.wrap(dev_batches[0][0]._t.clone())
         gy = lf.Tensor.wrap(dev_batches[0][1]._t.clone())
         c_before = sum(lf.launch_counts())
-        runner = lf.cuda.GraphedStep(lambda: train_step(gx, gy), opt, inputs=(gx, gy), warmup=2,
-                                     pdl=True)
+        try:
+            runner = lf.cuda.GraphedStep(lambda: train_step(gx, gy), opt, inputs=(gx, gy), warmup=2,
+                                         pdl=True)
+        except Exception as e:      # capture refused on this machine: every rank goes eager
+            print("bench: graph capture failed (%r), running eagerly" % (e,), file=sys.stderr)
+            runner = None
+        if world > 1:               # all ranks replay, or none does
+            ok = torch.tensor([1 if runner is not None else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                runner = None
         # two eager warm-up steps and the capture each went through the launchers once: a
         # third of the difference is the number of this package's kernels inside the graph
-        kernels_per_replay = (sum(lf.launch_counts()) - c_before) // 3
+        kernels_per_replay = (sum(lf.launch_counts()) - c_before) // 3 if runner is not None else 0
 
     def step_resident(i):
         x, y = dev_batches[i % n_pool]
@@ -170,7 +182,7 @@ def run_ours(args):
             "config": bench_config(args.config, model.num_params(), B, S, world),
             "engine": {"params": model.num_params(), "dp_mode": ddp.mode, "nvls": bool(ddp.nvls),
                        "state_sharded": ddp.arena.state_shards is not None,
-                       "buckets": len(ddp.buckets), "cuda_graph": bool(args.graph)},
+                       "buckets": len(ddp.buckets), "cuda_graph": runner is not None},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 4, "d2h_bytes_per_step": 4,
                     "final_loss": loss_val},
