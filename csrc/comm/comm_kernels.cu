@@ -275,8 +275,10 @@ struct KArgs {
   int* status;
 };
 
-template <int WORLD>  // 0 = runtime world size
-__global__ void __launch_bounds__(THREADS)
+// WORLD: 0 = runtime world size.  OPT (optimizer body) and NVLS are compile-time so that each
+// variant keeps only its own state in registers: two 512-thread CTAs per SM need <= 64.
+template <int WORLD, int OPT, bool NVLS>
+__global__ void __launch_bounds__(THREADS, 2)
 allreduce_adamw_kernel(const KArgs k) {
   __shared__ int sh_fail;
   __shared__ uint64_t sh_grad[MAX_WORLD], sh_shadow[MAX_WORLD];
@@ -295,17 +297,17 @@ allreduce_adamw_kernel(const KArgs k) {
 
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
-  const bool sharded = k.mode == COMM_TWO_SHOT_SHARDED;
-  const bool nvls = sharded && k.grad_mc != nullptr;
+  const bool sharded = NVLS || k.mode == COMM_TWO_SHOT_SHARDED;
+  constexpr bool nvls = NVLS;
   const long long span = sharded ? k.n / world : k.n;
   const long long base = k.elem_offset + (sharded ? (long long)k.rank * span : 0);
   for (long long i = skip ? span : tid; i < span / 8; i += nthreads) {
     const long long e = base + i * 8;          // arena coordinate (gradients, shadow, segments)
     const long long es = k.state_base + i * 8; // optimizer-state coordinate
     Adam8State st;
-    if (k.opt_kind == COMM_OPT_ADAMW) st = adam8_load(k.master, k.m, k.v, es);  // HBM reads go out first
+    if (OPT == COMM_OPT_ADAMW) st = adam8_load(k.master, k.m, k.v, es);  // HBM reads go out first
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (nvls) {
+    if constexpr (nvls) {
       const uint4 r = multimem_ld_reduce_bf16x8(k.grad_mc + e);
       acc_bf16x8(r, g);
     } else {
@@ -327,7 +329,7 @@ allreduce_adamw_kernel(const KArgs k) {
       }
     }
     float p[8];
-    if (k.opt_kind == COMM_OPT_ADAMW) {
+    if (OPT == COMM_OPT_ADAMW) {
       const float wd = k.nseg > 0 ? k.seg_wd[find_segment(k.seg_end, k.nseg, e)] : 0.0f;
       adam8(k.master, k.m, k.v, es, st, g, wd, adam, p);
     } else {
@@ -335,7 +337,7 @@ allreduce_adamw_kernel(const KArgs k) {
     }
     const uint4 packed = pack_bf16x8(p);
     if (sharded) {
-      if (nvls && k.shadow_mc) {
+      if (nvls) {
         multimem_st16(k.shadow_mc + e, packed);
       } else {
 #pragma unroll
@@ -473,12 +475,27 @@ cudaError_t allreduce_adamw(const CommAdamArgs& a, cudaStream_t stream) {
   k.budget = DEFAULT_BUDGET; k.status = a.status;
   const long long span = a.mode == COMM_TWO_SHOT_SHARDED ? a.n / a.world : a.n;
   const int blocks = pick_blocks(span / 8, a.max_blocks);
+  // NVLS needs both multicast addresses (reduce through ld_reduce, publish through st)
+  const bool nvls = k.grad_mc != nullptr && k.shadow_mc != nullptr;
+  if (!nvls) { k.grad_mc = nullptr; k.shadow_mc = nullptr; }
+#define LT_LAUNCH_COMM(W)                                                                           \
+  do {                                                                                              \
+    if (nvls) {                                                                                     \
+      if (a.opt_kind == COMM_OPT_ADAMW) allreduce_adamw_kernel<0, COMM_OPT_ADAMW, true><<<blocks, THREADS, 0, stream>>>(k); \
+      else allreduce_adamw_kernel<0, COMM_OPT_SGD, true><<<blocks, THREADS, 0, stream>>>(k);        \
+    } else if (a.opt_kind == COMM_OPT_ADAMW) {                                                      \
+      allreduce_adamw_kernel<W, COMM_OPT_ADAMW, false><<<blocks, THREADS, 0, stream>>>(k);          \
+    } else {                                                                                        \
+      allreduce_adamw_kernel<W, COMM_OPT_SGD, false><<<blocks, THREADS, 0, stream>>>(k);            \
+    }                                                                                               \
+  } while (0)
   switch (a.world) {
-    case 2: allreduce_adamw_kernel<2><<<blocks, THREADS, 0, stream>>>(k); break;
-    case 4: allreduce_adamw_kernel<4><<<blocks, THREADS, 0, stream>>>(k); break;
-    case 8: allreduce_adamw_kernel<8><<<blocks, THREADS, 0, stream>>>(k); break;
-    default: allreduce_adamw_kernel<0><<<blocks, THREADS, 0, stream>>>(k); break;
+    case 2: LT_LAUNCH_COMM(2); break;
+    case 4: LT_LAUNCH_COMM(4); break;
+    case 8: LT_LAUNCH_COMM(8); break;
+    default: LT_LAUNCH_COMM(0); break;
   }
+#undef LT_LAUNCH_COMM
   g_comm_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
