@@ -182,7 +182,10 @@ def run_ours(args):
             "config": bench_config(args.config, model.num_params(), B, S, world),
             "engine": {"params": model.num_params(), "dp_mode": ddp.mode, "nvls": bool(ddp.nvls),
                        "state_sharded": ddp.arena.state_shards is not None,
-                       "buckets": len(ddp.buckets), "cuda_graph": runner is not None},
+                       "buckets": len(ddp.buckets), "cuda_graph": runner is not None,
+                       # fp32 master + two moments held by THIS rank, and the allocator's peak
+                       "optimizer_state_gb": round(3 * 4 * ddp.arena.state_numel() / 1e9, 3),
+                       "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2)},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 4, "d2h_bytes_per_step": 4,
                     "final_loss": loss_val},

@@ -61,6 +61,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--csv", default="")
     ap.add_argument("--shape", default="", help="gemm only: M,N,K override")
+    ap.add_argument("--adamw-params", type=int, default=163_000_064,
+                    help="adamw only: parameter count (a smaller one keeps an ncu capture short)")
     args = ap.parse_args(argv)
     from luatorch_b200 import _backend as B
     C = B.ext()
@@ -124,6 +126,9 @@ def main(argv=None):
         add("softmax_ce", "CE fwd [%d,%d] bf16" % (rows_, cols), timer(lambda: C.cross_entropy_forward(logits, cols, labels), True), 0, nb)
         add("softmax_ce", "CE bwd in place [%d,%d] bf16" % (rows_, cols),
             timer(lambda: C.cross_entropy_backward(logits, cols, labels, lse, 1.0 / rows_, None, logits), True), 0, 2 * nb)
+        logits2 = torch.randn(rows_, ld, device="cuda").to(bf)
+        add("softmax_ce", "CE fused fwd+bwd in place [%d,%d] bf16" % (rows_, cols),
+            timer(lambda: C.cross_entropy_fused(logits2, cols, labels, 1.0 / rows_), True), 0, 2 * nb)
     if not only or "elementwise" in only:
         n = 1 << 28
         a = torch.randn(n, device="cuda").to(bf)
@@ -132,13 +137,13 @@ def main(argv=None):
         add("elementwise", "gelu bf16 2^28", timer(lambda: C.unary(8, a), True), 0, 2 * n * 2)
         add("elementwise", "sum bf16 2^28", timer(lambda: C.reduce(0, a, 1.0), True), 0, n * 2)
     if not only or "adamw" in only:
-        n = 163_000_064
+        n = args.adamw_params // 8 * 8
         master = torch.randn(n, device="cuda")
         shadow = torch.empty(n, device="cuda", dtype=bf)
         grad = torch.randn(n, device="cuda").to(bf)
         m = torch.zeros(n, device="cuda")
         v = torch.zeros(n, device="cuda")
-        add("adamw", "flat AdamW 163M params (bf16 grad, bf16 shadow)",
+        add("adamw", "flat AdamW %dM params (bf16 grad, bf16 shadow)" % (n // 1_000_000),
             timer(lambda: C.adamw_flat(master, shadow, grad, m, v, None, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.05, 1.0, None), True),
             0, n * 28.0)
     if not only or "embedding" in only:
