@@ -43,57 +43,125 @@ __device__ __forceinline__ MaxSum ms_block(MaxSum v, float* sh_m, float* sh_s) {
   return r;
 }
 
-// Online max / sum-exp over one row (vectorised when the row start is 16-byte aligned).
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// A row of `cols` elements starting at any element-aligned address splits into `head`
+// leading elements (up to the first 16-byte boundary), `nvec` 16-byte vectors and a tail,
+// so rows whose leading dimension is odd (a vocabulary of 50257 columns) still move as
+// 16-byte accesses.
 template <typename T>
-__device__ __forceinline__ MaxSum row_maxsum(const T* row, int64_t cols, bool vec_ok) {
-  constexpr int V = VecIO<T>::N;
-  MaxSum acc{-INFINITY, 0.0f};
-  int64_t done = 0;
-  if (vec_ok) {
-    const int64_t nvec = cols / V;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-      float x[V];
-      VecIO<T>::load(row + i * V, x);
-      float mx = x[0];
-#pragma unroll
-      for (int j = 1; j < V; ++j) mx = fmaxf(mx, x[j]);
-      if (mx > acc.m) { acc.s *= __expf(acc.m - mx); acc.m = mx; }
-      if (acc.m != -INFINITY) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) acc.s += __expf(x[j] - acc.m);
-      }
-    }
-    done = nvec * V;
+struct RowSplit {
+  int head, nvec;
+  __device__ __forceinline__ RowSplit(const T* row, int64_t cols) {
+    constexpr int V = VecIO<T>::N;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(row) & 15) / sizeof(T));
+    int h = mis ? V - mis : 0;
+    if (h > cols) h = (int)cols;
+    head = h;
+    nvec = (int)((cols - h) / V);
   }
-  for (int64_t i = done + threadIdx.x; i < cols; i += blockDim.x) ms_push(acc, VecIO<T>::ld(row + i));
+  __device__ __forceinline__ int64_t tail_begin() const { return head + (int64_t)nvec * VecIO<T>::N; }
+};
+
+// Online max / sum-exp over one row: one read, in the exp2 domain (one FFMA and one MUFU per
+// element); the running maximum moves only when a whole vector beats it.
+template <typename T>
+__device__ __forceinline__ MaxSum row_maxsum(const T* row, int64_t cols) {
+  constexpr int V = VecIO<T>::N;
+  const RowSplit<T> sp(row, cols);
+  MaxSum acc{-INFINITY, 0.0f};
+  if ((int)threadIdx.x < sp.head) ms_push(acc, VecIO<T>::ld(row + threadIdx.x));
+  const T* vrow = row + sp.head;
+  float c = acc.m == -INFINITY ? 0.0f : -acc.m * LOG2E;   // exponent offset of the running max
+  float s0 = acc.s, s1 = 0.0f;
+  for (int i = threadIdx.x; i < sp.nvec; i += blockDim.x) {
+    float x[V];
+    VecIO<T>::unpack(VecIO<T>::load_raw(vrow + (int64_t)i * V), x);
+    float mx = x[0];
+#pragma unroll
+    for (int j = 1; j < V; ++j) mx = fmaxf(mx, x[j]);
+    if (mx > acc.m) {
+      const float f = ex2_fast(fmaf(acc.m == -INFINITY ? 0.0f : acc.m, LOG2E, -mx * LOG2E));
+      s0 *= f; s1 *= f;
+      acc.m = mx;
+      c = -mx * LOG2E;
+    }
+#pragma unroll
+    for (int j = 0; j < V; j += 2) {
+      s0 += ex2_fast(fmaf(x[j], LOG2E, c));
+      s1 += ex2_fast(fmaf(x[j + 1], LOG2E, c));
+    }
+  }
+  acc.s = s0 + s1;
+  for (int64_t i = sp.tail_begin() + threadIdx.x; i < cols; i += blockDim.x) ms_push(acc, VecIO<T>::ld(row + i));
   return acc;
+}
+
+// Second pass shared by the softmax / cross-entropy kernels: out[i] = exp(x[i] - l) * gs,
+// minus gs at column `lab` (lab < 0: no label).  `in` and `out` may be the same row; they
+// must share their misalignment within 16 bytes for the vector path.
+template <typename T>
+__device__ __forceinline__ void row_exp_scale(const T* in, T* out, int64_t cols, float l, float gs,
+                                              int64_t lab) {
+  constexpr int V = VecIO<T>::N;
+  const float c = -l * LOG2E;
+  const bool same_mis = ((reinterpret_cast<uintptr_t>(in) ^ reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const RowSplit<T> sp(in, same_mis ? cols : 0);
+  int64_t first_tail = 0;
+  if (same_mis) {
+    if ((int)threadIdx.x < sp.head) {
+      float pj = ex2_fast(fmaf(VecIO<T>::ld(in + threadIdx.x), LOG2E, c));
+      if ((int64_t)threadIdx.x == lab) pj -= 1.0f;
+      VecIO<T>::st(out + threadIdx.x, pj * gs);
+    }
+    const T* vin = in + sp.head;
+    T* vout = out + sp.head;
+    const int64_t vlab = lab - sp.head;
+    const int lab_vec = vlab >= 0 ? (int)(vlab / V) : -1;
+    // a positive scale folds into the exponent: exp2(x*log2e - l*log2e + log2(gs))
+    const bool fold = gs > 0.0f;
+    const float cf = fold ? c + __log2f(gs) : c;
+    const float mul = fold ? 1.0f : gs;
+    for (int i = threadIdx.x; i < sp.nvec; i += blockDim.x) {
+      float x[V];
+      VecIO<T>::unpack(VecIO<T>::load_raw(vin + (int64_t)i * V), x);
+      if (fold) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) x[j] = ex2_fast(fmaf(x[j], LOG2E, cf));
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) x[j] = ex2_fast(fmaf(x[j], LOG2E, cf)) * mul;
+      }
+      if (i == lab_vec) {
+        const int jl = (int)(vlab - (int64_t)lab_vec * V);
+#pragma unroll
+        for (int j = 0; j < V; ++j) if (j == jl) x[j] -= gs;
+      }
+      VecIO<T>::store(vout + (int64_t)i * V, x);
+    }
+    first_tail = sp.tail_begin();
+  }
+  for (int64_t i = first_tail + threadIdx.x; i < cols; i += blockDim.x) {
+    float pj = ex2_fast(fmaf(VecIO<T>::ld(in + i), LOG2E, c));
+    if (i == lab) pj -= 1.0f;
+    VecIO<T>::st(out + i, pj * gs);
+  }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
-softmax_rows_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t cols, int64_t ld,
-                    int vec_base_ok) {
+softmax_rows_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t cols, int64_t ld) {
   __shared__ float sh_m[32], sh_s[32];
-  constexpr int V = VecIO<T>::N;
   const T* row = in + blockIdx.x * ld;
   T* orow = out + blockIdx.x * ld;
-  const bool vec_ok = vec_base_ok && (ld % V == 0);
-  MaxSum ms = ms_block(row_maxsum<T>(row, cols, vec_ok), sh_m, sh_s);
-  const float inv = 1.0f / ms.s;
-  int64_t done = 0;
-  if (vec_ok) {
-    const int64_t nvec = cols / V;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-      float x[V];
-      VecIO<T>::load(row + i * V, x);
-#pragma unroll
-      for (int j = 0; j < V; ++j) x[j] = __expf(x[j] - ms.m) * inv;
-      VecIO<T>::store(orow + i * V, x);
-    }
-    done = nvec * V;
-  }
-  for (int64_t i = done + threadIdx.x; i < cols; i += blockDim.x)
-    VecIO<T>::st(orow + i, __expf(VecIO<T>::ld(row + i) - ms.m) * inv);
+  MaxSum ms = ms_block(row_maxsum<T>(row, cols), sh_m, sh_s);
+  row_exp_scale<T>(row, orow, cols, ms.m, 1.0f / ms.s, -1);
 }
 
 // Attention scores: in-place softmax over bf16 rows, columns beyond the diagonal masked
@@ -150,13 +218,12 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS)
 ce_forward_kernel(const T* __restrict__ logits, int64_t ld, const void* __restrict__ labels,
                   int label_kind, int64_t cols, float* __restrict__ lse,
-                  float* __restrict__ row_loss, int* err_flag, int vec_base_ok) {
+                  float* __restrict__ row_loss, int* err_flag) {
   pdl_enter();
   __shared__ float sh_m[32], sh_s[32];
   const int64_t r = blockIdx.x;
   const T* row = logits + r * ld;
-  const bool vec_ok = vec_base_ok && (ld % VecIO<T>::N == 0);
-  MaxSum ms = ms_block(row_maxsum<T>(row, cols, vec_ok), sh_m, sh_s);
+  MaxSum ms = ms_block(row_maxsum<T>(row, cols), sh_m, sh_s);
   if (threadIdx.x == 0) {
     const float l = ms.m + __logf(ms.s);
     lse[r] = l;
@@ -175,38 +242,13 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS)
 ce_backward_kernel(const T* logits, int64_t ld, const void* __restrict__ labels, int label_kind,
                    int64_t cols, const float* __restrict__ lse, float grad_scale,
-                   const float* __restrict__ gs_dev, T* dlogits, int64_t ld_out,
-                   int vec_base_ok) {
+                   const float* __restrict__ gs_dev, T* dlogits, int64_t ld_out) {
   pdl_enter();
-  constexpr int V = VecIO<T>::N;
   const int64_t r = blockIdx.x;
-  const T* row = logits + r * ld;
-  T* orow = dlogits + r * ld_out;
-  const float l = lse[r];
   const float gs = gs_dev ? grad_scale * gs_dev[0] : grad_scale;
-  const int64_t lab = read_label(labels, label_kind, r);
-  const bool vec_ok = vec_base_ok && (ld % V == 0) && (ld_out % V == 0);
-  int64_t done = 0;
-  if (vec_ok) {
-    const int64_t nvec = cols / V;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-      float x[V];
-      VecIO<T>::load(row + i * V, x);
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float pj = __expf(x[j] - l);
-        if (i * V + j == lab) pj -= 1.0f;
-        x[j] = pj * gs;
-      }
-      VecIO<T>::store(orow + i * V, x);
-    }
-    done = nvec * V;
-  }
-  for (int64_t i = done + threadIdx.x; i < cols; i += blockDim.x) {
-    float pj = __expf(VecIO<T>::ld(row + i) - l);
-    if (i == lab) pj -= 1.0f;
-    VecIO<T>::st(orow + i, pj * gs);
-  }
+  int64_t lab = read_label(labels, label_kind, r);
+  if (lab >= cols) lab = -1;
+  row_exp_scale<T>(logits + r * ld, dlogits + r * ld_out, cols, lse[r], gs, lab);
 }
 
 // Forward and backward in one pass over the logits (training with the gradient written in
@@ -217,14 +259,12 @@ template <typename T>
 __global__ void __launch_bounds__(512)
 ce_fused_kernel(T* logits, int64_t ld, const void* __restrict__ labels, int label_kind,
                 int64_t cols, float* __restrict__ lse, float* __restrict__ row_loss, int* err_flag,
-                float grad_scale, int vec_base_ok) {
+                float grad_scale) {
   pdl_enter();
-  constexpr int V = VecIO<T>::N;
   __shared__ float sh_m[32], sh_s[32];
   const int64_t r = blockIdx.x;
   T* row = logits + r * ld;
-  const bool vec_ok = vec_base_ok && (ld % V == 0);
-  MaxSum ms = ms_block(row_maxsum<T>(row, cols, vec_ok), sh_m, sh_s);
+  MaxSum ms = ms_block(row_maxsum<T>(row, cols), sh_m, sh_s);
   const float l = ms.m + __logf(ms.s);
   int64_t lab = read_label(labels, label_kind, r);
   const bool bad = lab < 0 || lab >= cols;
@@ -238,28 +278,7 @@ ce_fused_kernel(T* logits, int64_t ld, const void* __restrict__ labels, int labe
     }
   }
   __syncthreads();   // the label's logit has been read before the row is overwritten
-  if (bad) lab = -1;
-  int64_t done = 0;
-  if (vec_ok) {
-    const int64_t nvec = cols / V;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-      float x[V];
-      VecIO<T>::load(row + i * V, x);
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float pj = __expf(x[j] - l);
-        if (i * V + j == lab) pj -= 1.0f;
-        x[j] = pj * grad_scale;
-      }
-      VecIO<T>::store(row + i * V, x);
-    }
-    done = nvec * V;
-  }
-  for (int64_t i = done + threadIdx.x; i < cols; i += blockDim.x) {
-    float pj = __expf(VecIO<T>::ld(row + i) - l);
-    if (i == lab) pj -= 1.0f;
-    VecIO<T>::st(row + i, pj * grad_scale);
-  }
+  row_exp_scale<T>(row, row, cols, l, grad_scale, bad ? -1 : lab);
 }
 
 template <typename T>
@@ -280,9 +299,8 @@ pointwise_loss_bwd_kernel(const T* __restrict__ pred, const T* __restrict__ targ
 cudaError_t softmax_rows(int dtype, const void* in, void* out, int64_t rows, int64_t cols,
                          int64_t ld, cudaStream_t s) {
   if (rows <= 0 || cols <= 0) return cudaSuccess;
-  const int vec = is_aligned16(in) && is_aligned16(out);
   LT_DISPATCH_DTYPE(dtype, T, {
-    softmax_rows_kernel<T><<<(unsigned)rows, THREADS, 0, s>>>((const T*)in, (T*)out, cols, ld, vec);
+    softmax_rows_kernel<T><<<(unsigned)rows, THREADS, 0, s>>>((const T*)in, (T*)out, cols, ld);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })
@@ -313,10 +331,9 @@ cudaError_t cross_entropy_forward(int dtype, const void* logits, int64_t ld, con
                                   int label_kind, int64_t rows, int64_t cols, float* lse,
                                   float* row_loss, int* err_flag, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
-  const int vec = is_aligned16(logits);
   LT_DISPATCH_DTYPE(dtype, T, {
     launch_pdl(ce_forward_kernel<T>, dim3((unsigned)rows), dim3(THREADS), 0, s, (const T*)logits, ld,
-               labels, label_kind, cols, lse, row_loss, err_flag, vec);
+               labels, label_kind, cols, lse, row_loss, err_flag);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })
@@ -327,10 +344,9 @@ cudaError_t cross_entropy_fused(int dtype, void* logits, int64_t ld, const void*
                                 int label_kind, int64_t rows, int64_t cols, float* lse,
                                 float* row_loss, int* err_flag, float grad_scale, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
-  const int vec = is_aligned16(logits);
   LT_DISPATCH_DTYPE(dtype, T, {
     launch_pdl(ce_fused_kernel<T>, dim3((unsigned)rows), dim3(512), 0, s, (T*)logits, ld, labels,
-               label_kind, cols, lse, row_loss, err_flag, grad_scale, vec);
+               label_kind, cols, lse, row_loss, err_flag, grad_scale);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })
@@ -342,10 +358,9 @@ cudaError_t cross_entropy_backward(int dtype, const void* logits, int64_t ld, co
                                    float grad_scale, const float* gs_dev, void* dlogits,
                                    int64_t ld_out, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
-  const int vec = is_aligned16(logits) && is_aligned16(dlogits);
   LT_DISPATCH_DTYPE(dtype, T, {
     launch_pdl(ce_backward_kernel<T>, dim3((unsigned)rows), dim3(THREADS), 0, s, (const T*)logits, ld,
-               labels, label_kind, cols, lse, grad_scale, gs_dev, (T*)dlogits, ld_out, vec);
+               labels, label_kind, cols, lse, grad_scale, gs_dev, (T*)dlogits, ld_out);
     LT_COUNT_LAUNCH();
     return cudaGetLastError();
   })

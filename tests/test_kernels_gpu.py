@@ -207,7 +207,7 @@ def test_reductions(C, n):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_softmax_and_cross_entropy(C, rows, cols, dtype):
     torch.manual_seed(6)
-    ld = (cols + 7) // 8 * 8
+    ld = (cols + 7) // 8 * 8 if rows % 2 == 0 else cols + 1   # odd row counts: rows not 16-byte aligned
     full = (torch.randn(rows, ld, device="cuda") * 3).to(dtype)
     logits = full[:, :cols]
     labels = torch.randint(0, cols, (rows,), device="cuda")
@@ -230,9 +230,11 @@ def test_softmax_and_cross_entropy(C, rows, cols, dtype):
     assert word[0] == 1 and word[1] == 0 and word[2] == cols      # flag, row, offending label
 
 
-@pytest.mark.parametrize("rows,cols,ld", [(64, 1000, 1000), (33, 50257, 50264)])
+@pytest.mark.parametrize("rows,cols,ld", [(64, 1000, 1000), (33, 50257, 50264), (19, 50257, 50257),
+                                          (21, 1003, 1005)])
 def test_cross_entropy_fused_forward_backward(C, rows, cols, ld):
-    """One kernel: loss + log-sum-exp, logits overwritten by (softmax - onehot) * scale."""
+    """One kernel: loss + log-sum-exp, logits overwritten by (softmax - onehot) * scale.
+    Odd leading dimensions start every row at another offset within 16 bytes."""
     torch.manual_seed(4)
     buf = torch.zeros(rows, ld, device="cuda", dtype=torch.bfloat16)
     buf[:, :cols] = (torch.randn(rows, cols, device="cuda") * 2).bfloat16()
@@ -336,7 +338,8 @@ def test_embedding(C, dtype):
     torch.testing.assert_close(dp, ref_dp, atol=1e-4, rtol=1e-4)
     bad = ids.clone()
     bad[3] = vocab + 1
-    assert C.embedding_forward(table, bad, None, 1)[1].item() == 1
+    word = C.embedding_forward(table, bad, None, 1)[1].tolist()
+    assert word[0] == 1 and word[1] == 3 and word[2] == vocab + 1     # flag, position, offending id
 
 
 def test_im2col_col2im(C):
