@@ -19,9 +19,11 @@ per parameter (ddp.lua:48-61).  This one is real:
                      arena (reduce-scatter + shard optimizer + all-gather in one launch).
                      The optimizer state is sharded in MEMORY too: each rank allocates
                      1/world of master / m / v (`shard_state=False` keeps them full length).
-                     With NVLS (`nvls`, default on where the buffers have a multicast
-                     address) the slice is read with multimem.ld_reduce and published with
-                     multimem.st: the NVSwitch reduces and replicates;
+                     With NVLS (`nvls`; default: on from 4 ranks where the buffers have a
+                     multicast address, `LT_NVLS=1/0` forces it) the slice is read with
+                     multimem.ld_reduce and published with multimem.st: the NVSwitch reduces
+                     and replicates.  Between 2 ranks plain peer loads are faster (measured:
+                     32 MB bucket 0.079 ms against 0.106 ms), so NVLS stays off there;
         "replicated" one-shot: every rank reduces the whole bucket and updates its full
                      replica (least latency; meant for small models);
         "auto"       "replicated" when the whole model is one small bucket (<= 4 MB of bf16
@@ -115,7 +117,13 @@ class DDP:
         bucket_elems = max(2048, int(bucket_mb * 1024 * 1024 / 2))
         self.buckets = self.arena.buckets(bucket_elems)
         # NVLS: multicast addresses of the two arenas (sharded mode only)
-        want_nvls = (os.environ.get("LT_NVLS", "1") != "0") if nvls is None else bool(nvls)
+        env_nvls = os.environ.get("LT_NVLS")
+        if nvls is not None:
+            want_nvls = bool(nvls)
+        elif env_nvls is not None:
+            want_nvls = env_nvls != "0"
+        else:
+            want_nvls = self.world >= 4
         self.grad_mc = self.shadow_mc = 0
         if (want_nvls and on_gpu and self.peer and self.mode == "sharded" and
                 self.grad_buf.multicast_ptr and self.shadow_buf.multicast_ptr):
