@@ -71,6 +71,11 @@ Tensor scratch_floats(int64_t n, const Tensor& like) {
 }
 
 // ------------------------------------------------------------------------------ GEMM
+// One-shot hint consumed by the next gemm() call: that product is independent of the `n`
+// kernels launched just before it (lt::GemmArgs::overlap_prev).
+static int g_next_gemm_overlap = 0;
+void gemm_next_overlaps_prev(int64_t n) { g_next_gemm_overlap = (int)n; }
+
 void gemm(const Tensor& A, const Tensor& B, Tensor& C, int64_t M, int64_t N, int64_t K,
           int64_t lda, int64_t ldb, int64_t ldc, bool a_mn, bool b_mn, int64_t batch_inner,
           int64_t batch_outer, int64_t a_si, int64_t a_so, int64_t b_si, int64_t b_so,
@@ -109,6 +114,8 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, int64_t M, int64_t N, int
   if (aux_out.has_value()) g.aux_out = aux_out->data_ptr();
   if (aux_in.has_value()) { g.aux_in = aux_in->data_ptr(); g.ld_aux = ld_aux; }
   g.causal_tiles = (int)causal_tiles;
+  g.overlap_prev = g_next_gemm_overlap;
+  g_next_gemm_overlap = 0;
   // scratch for split-K comes from torch's caching allocator, so it is stream-ordered
   Tensor ws;
   const size_t ws_bytes = lt::gemm_split_k_workspace_bytes(g);
@@ -517,8 +524,10 @@ Tensor im2col(const Tensor& in, int64_t batch, int64_t C, int64_t H, int64_t W, 
   const int64_t oh = (H + 2 * pad - k) / stride + 1, ow = (W + 2 * pad - k) / stride + 1;
   const int64_t patch = C * k * k;
   if (ld < patch) ld = patch;
-  Tensor cols = ld == patch ? at::empty({batch * oh * ow, patch}, in.options())
-                            : at::zeros({batch * oh * ow, ld}, in.options());
+  // the 16-byte-store kernel writes the padding columns itself; the scalar one leaves them
+  const bool vec = ld % (16 / (int64_t)in.element_size()) == 0;
+  Tensor cols = (ld == patch || vec) ? at::empty({batch * oh * ow, ld}, in.options())
+                                     : at::zeros({batch * oh * ow, ld}, in.options());
   check(lt::im2col(dt(in), in.data_ptr(), cols.data_ptr(), (int)batch, (int)C, (int)H, (int)W,
                    (int)k, (int)stride, (int)pad, ld, cur_stream()), "im2col");
   return cols;
@@ -753,6 +762,7 @@ std::vector<int64_t> launch_counts() {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_next_overlaps_prev", &gemm_next_overlaps_prev);
   m.def("gemm_gather", &gemm_gather);
   m.def("gemm_device_error", &gemm_device_error);
   m.def("binary", &binary);

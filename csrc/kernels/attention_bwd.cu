@@ -65,6 +65,7 @@ struct BwdParams {
   __nv_bfloat16* out1;  // dV (kernel 2)
   long long o1_sb, o1_ss, o1_sh;
   __nv_bfloat16* ds_out;  // optional [B, H, S, S]: dS tiles for the dQ GEMM (dK/dV kernel only)
+  int late_wait = 0;      // independent of the previous kernel: wait for it before exit (common.cuh)
 };
 
 // ------------------------------------------------------------------ delta = rowsum(dO * O)
@@ -259,12 +260,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tmem_alloc(smem_u32(tmem_holder), 512);
     tmem_relinquish();
   }
-  pdl_trigger();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  pdl_wait();   // operands come from earlier kernels of the stream
+  pdl_enter();   // operands come from earlier kernels of the stream
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128;
   const uint32_t tmem_acc0 = tmem_base + 256;        // dK or dQ
   const uint32_t tmem_acc1 = tmem_base + 256 + D;    // dV
@@ -593,12 +593,13 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_cons
     tmem_alloc(smem_u32(tmem_holder), L::TMEM_COLS);
     tmem_relinquish();
   }
-  pdl_trigger();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  pdl_wait();   // operands come from earlier kernels of the stream
+  // operands come from kernels before the previous one when `late_wait` is set (the dQ kernel
+  // after the dK / dV kernel: both read q, k, v, dO, lse, delta and write disjoint outputs)
+  pdl_enter(p.late_wait != 0);
   const uint32_t tmem_s = tmem_base;             // 64 fp32 score columns; packed P lands in them
   const uint32_t tmem_dp = tmem_base + 64;       // 64 fp32 dP columns; packed dS lands in them
   const uint32_t tmem_acc0 = tmem_base + 128;    // dK (DKDV) or dQ: from dS
@@ -793,6 +794,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tm_fix0, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, L::TMEM_COLS);
   }
+  pdl_leave(p.late_wait != 0);
 }
 
 template <int D, bool DKDV>
@@ -883,7 +885,11 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
     if (e2 != cudaSuccess) return e2;
     p2.out0 = (__nv_bfloat16*)g.dq; p2.o0_sb = g.dq_sb; p2.o0_ss = g.dq_ss; p2.o0_sh = g.dq_sh;
     p2.out1 = nullptr; p2.o1_sb = p2.o1_ss = p2.o1_sh = 0;
-    return launch_bwd2<64, false>(q128, do128, k64, v64, p2, grid2, stream);
+    const LateWait lw = late_wait_begin(1);   // independent of the dK / dV kernel: runs in its tail
+    p2.late_wait = lw.on;
+    e2 = launch_bwd2<64, false>(q128, do128, k64, v64, p2, grid2, stream);
+    late_wait_commit(lw);
+    return e2;
   }
 
   CUtensorMap tq, tk, tv, tdo;

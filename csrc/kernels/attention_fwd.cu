@@ -223,12 +223,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tmem_alloc(smem_u32(tmem_holder), L::TMEM_COLS);
     tmem_relinquish();
   }
-  pdl_trigger();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  pdl_wait();   // q, k, v come from the previous kernel
+  pdl_enter();   // q, k, v come from the previous kernel
   const uint32_t tmem_s = tmem_base;                // NSB score buffers of 128 columns
   const uint32_t tmem_o = tmem_base + NSB * 128;    // D columns
 
@@ -617,12 +616,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tmem_alloc(smem_u32(tmem_holder), L::TMEM_COLS);
     tmem_relinquish();
   }
-  pdl_trigger();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  pdl_wait();   // q, k, v come from the previous kernel
+  pdl_enter();   // q, k, v come from the previous kernel
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + 128;
 

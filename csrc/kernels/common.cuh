@@ -18,17 +18,30 @@ extern std::atomic<uint64_t> g_ops_launches;
 // the kernel before it in the stream is still running, so its launch latency and prologue
 // overlap that kernel's tail; pdl_wait() then blocks until the earlier kernel has completed
 // and its writes are visible.  Rules: a kernel launched this way touches no global memory
-// before pdl_wait(), and pdl_trigger() (allow the NEXT kernel to be scheduled) may come first
-// because the next kernel waits for this one in the same way.  LT_PDL=0 in the environment
-// turns the launch attribute off (plain stream order); set_pdl_override() does it at run time.
+// before pdl_wait(), and every kernel calls pdl_trigger() (allow the NEXT kernel to be
+// scheduled) AFTER its own pdl_wait().  The dependent kernel is released once every CTA of
+// this one has triggered, so whenever it runs, everything BEFORE this kernel is complete.
+// A kernel that is independent of its immediate predecessor (a weight-gradient GEMM after the
+// input-gradient GEMM of the same layer) can therefore skip the wait in its prologue, work in
+// the predecessor's tail, and call pdl_wait() just before it exits, which keeps completion
+// transitive for the kernel after it ("late wait").  LT_PDL=0 in the environment turns the
+// launch attribute off (plain stream order); set_pdl_override() does it at run time.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
+}
+// late == true: the caller is independent of the previous kernel; pair with pdl_leave(late)
+__device__ __forceinline__ void pdl_enter(bool late) {
+  if (!late) pdl_wait();
+  pdl_trigger();
+}
+__device__ __forceinline__ void pdl_leave(bool late) {
+  if (late) pdl_wait();
 }
 
 // -1: follow LT_PDL; 0 / 1: forced off / on at run time (set_pdl_override in ops.h)
@@ -44,6 +57,31 @@ inline bool pdl_enabled() {
   return v != 0;
 }
 
+// LT_LATE_WAIT=0 makes every kernel wait for its predecessor in its prologue (comparison runs)
+inline bool late_wait_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LT_LATE_WAIT");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0 && pdl_enabled();
+}
+
+// Number of late-wait kernels launched back to back just before now (0 after any other launch
+// through launch_pdl).  A late-wait kernel triggers without having waited, so the kernel after
+// it can start while the one before it still runs: a kernel may therefore ask for late wait
+// only if it is independent of the previous `independent_of` launches and the chain of late
+// kernels in front of it is shorter than that.  late_wait_begin() decides, the caller launches
+// (which resets the chain) and calls late_wait_commit() when the launch was a late one.
+extern int g_late_chain;
+struct LateWait { int on, chain; };
+inline LateWait late_wait_begin(int independent_of) {
+  LateWait l{0, g_late_chain};
+  l.on = (late_wait_enabled() && independent_of > l.chain) ? 1 : 0;
+  return l;
+}
+inline void late_wait_commit(const LateWait& l) { if (l.on) g_late_chain = l.chain + 1; }
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {
@@ -57,6 +95,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  g_late_chain = 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -15,6 +15,7 @@ namespace lt {
 std::atomic<uint64_t> g_ops_launches{0};
 uint64_t ops_launch_count() { return g_ops_launches.load(); }
 int g_pdl_override = -1;
+int g_late_chain = 0;
 void set_pdl_override(int v) { g_pdl_override = v < 0 ? -1 : (v != 0); }
 
 namespace {

@@ -54,6 +54,12 @@ struct GemmArgs {
                          // 2: skip tiles strictly below (m0 > n0 + BN - 1)
   int causal_k = 0;      // 1: the k loop of the output tile at row m0 stops at k = m0 + 128
                          //    (A is lower block-triangular in 128-blocks: attention dS / P)
+  // n > 0: this product reads nothing that the n kernels launched just before it on `stream`
+  // write and writes nothing they touch (n = 1: the weight-gradient GEMM after the
+  // input-gradient GEMM of the same layer).  Under programmatic dependent launch it then works
+  // in their tail and waits for them only before it exits; everything older is complete by
+  // then (see the launch rules in common.cuh).  Without the launch attribute it does nothing.
+  int overlap_prev = 0;
   // Optional scratch for split-K (fp32, device memory valid on `stream`).  When a long-K
   // product has too few output tiles to fill the chip (weight gradients: K = tokens), K is cut
   // into S slices that run as S batches into workspace[S][M][N], and a second kernel sums the

@@ -100,6 +100,7 @@ struct KernelParams {
   long long g_ldb;
   int g_rank, g_world, g_rows_per_shard, g_done;
   uint32_t g_epoch;
+  int late_wait;   // GemmArgs::overlap_prev: wait for the previous kernel before exit, not before work
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -376,12 +377,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tmem_alloc(smem_u32(tmem_base_holder), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  pdl_trigger();   // the next kernel may be scheduled; it waits for this one in its own prologue
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_holder;
-  pdl_wait();      // everything above overlapped the previous kernel's tail; its results are final now
+  // Everything above overlapped the previous kernel's tail; after the wait its results are
+  // final.  The trigger comes AFTER the wait, so whenever a dependent kernel runs, everything
+  // before this kernel is complete: that is what lets a kernel marked `late_wait` (independent
+  // of its predecessor) start working at once and wait only before it exits.
+  if (!p.late_wait) pdl_wait();
+  pdl_trigger();
 
   const int num_kb = (p.K + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -548,6 +553,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+  if (p.late_wait) pdl_wait();   // this grid completes only after its predecessor has
 }
 
 // ------------------------------------------------------------------------------
@@ -739,12 +745,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_before_sync();
   __syncthreads();
-  pdl_trigger();
   cluster_arrive();          // the peer's barriers exist before anything is sent to them
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_holder;
-  pdl_wait();                // the previous kernel's results are final from here on
+  if (!p.late_wait) pdl_wait();   // the previous kernel's results are final from here on
+  pdl_trigger();                  // after the wait: see gemm_tcgen05_kernel
 
   const int num_kb = (p.K + BK * Cfg::KSUB - 1) / (BK * Cfg::KSUB);
   const int tiles_per_batch = p.tiles_m * p.tiles_n;     // tiles_m counts 256-row pair tiles
@@ -925,6 +931,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
+  if (p.late_wait) pdl_wait();
 }
 
 // ------------------------------------------------------------------------------
@@ -1066,6 +1073,7 @@ KernelParams make_params(const GemmArgs& a) {
   if (a.aux_out) w = w && a32(a.aux_out);
   if (a.aux_in) w = w && a32(a.aux_in) && a.ld_aux % 16 == 0;
   p.vec32_ok = w ? 1 : 0;
+  p.late_wait = 0;   // set by the launcher (launch_late)
   p.g_b_ptrs = nullptr; p.g_signal_ptrs = nullptr; p.g_flags = nullptr; p.g_status = nullptr;
   p.g_ldb = 0; p.g_rank = 0; p.g_world = 1; p.g_rows_per_shard = 0; p.g_done = 0; p.g_epoch = 0;
   if (a.gather && a.gather->world > 1) {
@@ -1109,7 +1117,10 @@ cudaError_t launch_tc(const GemmArgs& a, cudaStream_t stream) {
   if (!ok) return cudaErrorInvalidValue;
   const long long total = (long long)p.tiles_m * p.tiles_n * p.batch_total;
   const int grid = (int)(total < num_sms() ? total : num_sms());
+  const LateWait lw = late_wait_begin(a.overlap_prev);
+  p.late_wait = lw.on;
   cudaError_t le = launch_pdl(gemm_tcgen05_kernel<BN>, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, p);
+  late_wait_commit(lw);
   if (le != cudaSuccess) return le;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
@@ -1176,7 +1187,10 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   if (!ok) return cudaErrorInvalidValue;
   const long long total = (long long)p.tiles_m * p.tiles_n * p.batch_total;
   const int grid = 2 * (int)(total < clusters ? total : clusters);
+  const LateWait lw = late_wait_begin(a.overlap_prev);
+  p.late_wait = lw.on;
   cudaError_t le = launch_pdl(gemm_tcgen05_pair_kernel<BN>, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, p);
+  late_wait_commit(lw);
   if (le != cudaSuccess) return le;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
@@ -1294,7 +1308,7 @@ int choose_split(const GemmArgs& a, TileChoice* slice_tile) {
                           (a.batch_outer < 1 ? 1 : a.batch_outer);
   TileChoice whole = choose_tile(a, a.K, batch, a.c_fp32 != 0);
   *slice_tile = whole;
-  if (batch != 1 || a.bias || a.act != GEMM_ACT_NONE || a.residual || a.aux_out || a.aux_in ||
+  if (batch != 1 || a.act != GEMM_ACT_NONE || a.residual || a.aux_out || a.aux_in ||
       a.causal_tiles || a.causal_k || a.K < 2048 || getenv("LT_GEMM_NO_SPLIT"))
     return 1;
   // LT_GEMM_SPLIT=n forces a split factor (tuning aid): the slice tile still comes from the model
@@ -1309,8 +1323,8 @@ int choose_split(const GemmArgs& a, TileChoice* slice_tile) {
   }
   int best_s = 1;
   double best_cost = whole.cost;
-  const int splits[11] = {2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
-  for (int i = 0; i < 11; ++i) {
+  const int splits[14] = {2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 148};
+  for (int i = 0; i < 14; ++i) {
     const int s = splits[i];
     if (a.K % (s * BK) != 0 || a.K / s < 8 * BK) continue;
     TileChoice t = choose_tile(a, a.K / s, s, true);
@@ -1338,39 +1352,68 @@ cudaError_t launch_choice(const TileChoice& t, const GemmArgs& a, cudaStream_t s
   }
 }
 
-// C = sum_s ws[s] (+ C), four elements per thread; slices are added in index order.
+// C = sum_s ws[s] (+ bias) (+ C), four elements per thread; slices are added in index order.
+// The workspace rows are `ws_ld` floats apart (N rounded up to 4); C is written with 16-byte
+// accesses when `vec` says its rows allow it, element by element otherwise (N = 27 ...).
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slice, int M, int N,
-                     void* C, long long ldc, int c_fp32, int accumulate) {
+                     int ws_ld, void* C, long long ldc, int c_fp32, int accumulate,
+                     const void* __restrict__ bias, int bias_fp32, int vec) {
   pdl_enter();
-  const long long quads = (long long)M * (N / 4);
+  const int qpr = ws_ld / 4;
+  const long long quads = (long long)M * qpr;
   for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < quads;
        q += (long long)gridDim.x * blockDim.x) {
-    const long long row = q / (N / 4);
-    const int col = (int)(q - row * (N / 4)) * 4;
-    const float* src = ws + row * N + col;
+    const long long row = q / qpr;
+    const int col = (int)(q - row * qpr) * 4;
+    const float* src = ws + row * ws_ld + col;
     float4 acc = *reinterpret_cast<const float4*>(src);
     for (int s = 1; s < splits; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(src + s * slice);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
-    if (c_fp32) {
-      float4* dst = reinterpret_cast<float4*>((float*)C + row * ldc + col);
-      if (accumulate) { const float4 o = *dst; acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w; }
-      *dst = acc;
-    } else {
-      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)C + row * ldc + col);
-      if (accumulate) {
-        const float2 o0 = __bfloat1622float2(dst[0]), o1 = __bfloat1622float2(dst[1]);
-        acc.x += o0.x; acc.y += o0.y; acc.z += o1.x; acc.w += o1.y;
+    float r[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (col + j < N)
+          r[j] += bias_fp32 ? ((const float*)bias)[col + j]
+                            : __bfloat162float(((const __nv_bfloat16*)bias)[col + j]);
+    }
+    if (vec) {
+      if (c_fp32) {
+        float4* dst = reinterpret_cast<float4*>((float*)C + row * ldc + col);
+        if (accumulate) { const float4 o = *dst; r[0] += o.x; r[1] += o.y; r[2] += o.z; r[3] += o.w; }
+        *dst = make_float4(r[0], r[1], r[2], r[3]);
+      } else {
+        __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)C + row * ldc + col);
+        if (accumulate) {
+          const float2 o0 = __bfloat1622float2(dst[0]), o1 = __bfloat1622float2(dst[1]);
+          r[0] += o0.x; r[1] += o0.y; r[2] += o1.x; r[3] += o1.y;
+        }
+        dst[0] = __floats2bfloat162_rn(r[0], r[1]);
+        dst[1] = __floats2bfloat162_rn(r[2], r[3]);
       }
-      dst[0] = __floats2bfloat162_rn(acc.x, acc.y);
-      dst[1] = __floats2bfloat162_rn(acc.z, acc.w);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (col + j >= N) break;
+        if (c_fp32) {
+          float* d = (float*)C + row * ldc + col + j;
+          *d = accumulate ? *d + r[j] : r[j];
+        } else {
+          __nv_bfloat16* d = (__nv_bfloat16*)C + row * ldc + col + j;
+          *d = __float2bfloat16(accumulate ? __bfloat162float(*d) + r[j] : r[j]);
+        }
+      }
     }
   }
 }
 
-bool split_k_shape_ok(const GemmArgs& a) {
+// every output shape can be split; the workspace rows are padded to four floats
+bool split_k_shape_ok(const GemmArgs&) { return true; }
+inline int ws_ld_of(const GemmArgs& a) { return (a.N + 3) & ~3; }
+inline bool reduce_vec_ok(const GemmArgs& a) {
   return a.N % 4 == 0 && a.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(a.C) & 15) == 0;
 }
 
@@ -1380,12 +1423,18 @@ size_t gemm_split_k_workspace_bytes(const GemmArgs& a) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || !gemm_uses_tensor_cores(a) || !split_k_shape_ok(a)) return 0;
   TileChoice t;
   const int s = choose_split(a, &t);
-  return s > 1 ? (size_t)s * (size_t)a.M * (size_t)a.N * sizeof(float) : 0;
+  return s > 1 ? (size_t)s * (size_t)a.M * (size_t)ws_ld_of(a) * sizeof(float) : 0;
 }
 
-cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
-  if (a.M <= 0 || a.N <= 0) return cudaSuccess;
-  if (a.K <= 0) return cudaErrorInvalidValue;
+// True while the kernel launched last by gemm_bf16 is a split-K reduction (it reads the
+// workspace): a split-K GEMM that follows may then not start before that kernel has finished.
+static thread_local bool g_prev_reads_workspace = false;
+
+cudaError_t gemm_bf16(const GemmArgs& args, cudaStream_t stream) {
+  if (args.M <= 0 || args.N <= 0) return cudaSuccess;
+  if (args.K <= 0) return cudaErrorInvalidValue;
+  GemmArgs a = args;
+  if (a.gather && a.gather->world > 1) a.overlap_prev = 0;
   if (a.gather && a.gather->world > 1) {
     // B is gathered inside the kernel: CTA-pair path only
     const GemmGather& g = *a.gather;
@@ -1401,7 +1450,7 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (!gemm_uses_tensor_cores(a)) return launch_simt(a, stream);
   TileChoice tile;
   int splits = choose_split(a, &tile);
-  const size_t need = (size_t)splits * (size_t)a.M * (size_t)a.N * sizeof(float);
+  const size_t need = (size_t)splits * (size_t)a.M * (size_t)ws_ld_of(a) * sizeof(float);
   if (splits > 1 && (!a.workspace || a.workspace_bytes < need || !split_k_shape_ok(a))) {
     splits = 1;
     tile = choose_tile(a, a.K, 1, a.c_fp32 != 0);
@@ -1409,8 +1458,13 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (getenv("LT_GEMM_DEBUG"))
     fprintf(stderr, "gemm %dx%dx%d -> %s BN=%d split %d (model %.1f us)\n", a.M, a.N, a.K,
             tile.pair ? "pair" : "single", tile.bn, splits, tile.cost * 1e6);
-  if (splits == 1) return launch_choice(tile, a, stream);
+  if (splits == 1) {
+    g_prev_reads_workspace = false;
+    return launch_choice(tile, a, stream);
+  }
   // K slices as batches into the fp32 workspace, then one deterministic reduction
+  if (g_prev_reads_workspace) a.overlap_prev = 0;
+  g_prev_reads_workspace = true;
   GemmArgs g = a;
   const int ks = a.K / splits;
   g.K = ks;
@@ -1419,21 +1473,24 @@ cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   g.a_stride_inner = a.a_mn_major ? (int64_t)ks * a.lda : ks;
   g.b_stride_inner = a.b_mn_major ? (int64_t)ks * a.ldb : ks;
   g.a_stride_outer = g.b_stride_outer = 0;
+  const int ws_ld = ws_ld_of(a);
   g.C = a.workspace;
-  g.ldc = a.N;
-  g.c_stride_inner = (int64_t)a.M * a.N;
+  g.ldc = ws_ld;
+  g.c_stride_inner = (int64_t)a.M * ws_ld;
+  g.bias = nullptr;       // added by the reduction
   g.c_stride_outer = 0;
   g.c_fp32 = 1;
   g.accumulate = 0;
   g.workspace = nullptr;
   cudaError_t e = launch_choice(tile, g, stream);
   if (e != cudaSuccess) return e;
-  const long long quads = (long long)a.M * (a.N / 4);
+  const long long quads = (long long)a.M * (ws_ld / 4);
   int blocks = (int)((quads + 255) / 256);
   if (blocks > 8 * num_sms()) blocks = 8 * num_sms();
   cudaError_t re = launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream,
-                              (const float*)a.workspace, splits, (long long)a.M * a.N, a.M, a.N,
-                              a.C, (long long)a.ldc, a.c_fp32, a.accumulate);
+                              (const float*)a.workspace, splits, (long long)a.M * ws_ld, a.M, a.N,
+                              ws_ld, a.C, (long long)a.ldc, a.c_fp32, a.accumulate, a.bias,
+                              a.bias_fp32, reduce_vec_ok(a) ? 1 : 0);
   if (re != cudaSuccess) return re;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();

@@ -355,12 +355,15 @@ def dropout_backward(dy: torch.Tensor, p: float, ctx) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------ matmul family
 def gemm(a, b, *, a_t=False, b_t=False, out=None, out_dtype=None, alpha=1.0, accumulate=False,
-         bias=None, act=0, residual=None, aux_out=None, aux_in=None, n_valid=None, k_valid=None):
+         bias=None, act=0, residual=None, aux_out=None, aux_in=None, n_valid=None, k_valid=None,
+         overlap_prev=0):
     """C = act(alpha * op(a) @ op(b) + bias) + residual on the tensor cores (bf16 operands).
 
     a: [M, K] (or [K, M] when a_t), b: [K, N] (or [N, K] when b_t); both 2-d with unit inner
     stride (row strides may exceed the logical width).  `n_valid` restricts the logical N when
-    b is a padded buffer.
+    b is a padded buffer.  `overlap_prev=n`: the caller guarantees that this product reads
+    nothing the n kernels launched just before it write and writes nothing they touch (`out`
+    given, not freshly allocated); it then runs in their tail instead of after them.
     """
     C = ext()
     if a_t:
@@ -377,6 +380,8 @@ def gemm(a, b, *, a_t=False, b_t=False, out=None, out_dtype=None, alpha=1.0, acc
         K = k_valid
     if out is None:
         out = torch.empty((M, N), device=a.device, dtype=out_dtype or torch.bfloat16)
+    elif overlap_prev:
+        C.gemm_next_overlaps_prev(int(overlap_prev))
     C.gemm(a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), bool(a_t), not b_t,
            1, 1, 0, 0, 0, 0, 0, 0, float(alpha), bool(accumulate), bias, int(act), residual,
            residual.stride(0) if residual is not None else 0, aux_out, aux_in,

@@ -140,7 +140,9 @@ class Linear(Module):
                 gt = B.ext().unary_backward(B._UN[act], pre, gt)
             if gt.stride(-1) != 1:
                 gt = gt.contiguous()
+            dgrad_last = False      # the input-gradient GEMM is the kernel launched last
             if input.requires_grad:
+                dgrad_last = input.grad is None
                 if fuse_dact and input.grad is None:
                     in_act, in_pre, _ = input._act_ctx
                     autograd.acc_grad(input, B.gemm(gt, w, b_t=True, k_valid=N,
@@ -151,8 +153,11 @@ class Linear(Module):
             if weight.requires_grad:
                 if view_param is not None and view_param.grad is None:
                     weight.grad = None
+                # dW reads x and g only and writes its own arena slot: independent of the
+                # input-gradient GEMM just launched, so it may run in that kernel's tail
                 write_param_grad(weight, lambda o, acc: B.gemm(x, gt, a_t=True, out=o,
-                                                               accumulate=acc, n_valid=N))
+                                                               accumulate=acc, n_valid=N,
+                                                               overlap_prev=1 if dgrad_last else 0))
                 if view_param is not None:
                     view_param.grad = Tensor(_data=weight.grad._t[:, :N])
             if bias_p is not None and bias_p.requires_grad and not bias_folded[0]:

@@ -249,6 +249,34 @@ def test_cross_entropy_fused_forward_backward(C, rows, cols, ld):
     torch.testing.assert_close(buf[:, :cols].float(), x.grad, atol=2e-4, rtol=3e-2)
 
 
+@pytest.mark.parametrize("dtype,B,Cc,H,W,k,stride,pad,ld", [
+    (torch.bfloat16, 4, 32, 32, 32, 3, 2, 1, 288),     # conv net layer 2: 16-byte rows
+    (torch.bfloat16, 2, 3, 32, 32, 3, 1, 1, 32),       # layer 1: patch 27 padded to 32
+    (torch.bfloat16, 3, 64, 16, 16, 3, 2, 1, 576),
+    (torch.float32, 3, 5, 9, 11, 3, 2, 1, 48),
+    (torch.float32, 2, 4, 12, 10, 5, 1, 2, 100),
+])
+def test_im2col_col2im_vector_paths(C, dtype, B, Cc, H, W, k, stride, pad, ld):
+    """The 16-byte-store im2col (padding columns zeroed by the kernel) and the col2im that
+    stages the contributing cols rows in shared memory, against unfold / fold in fp32."""
+    torch.manual_seed(12)
+    x = torch.randn(B, Cc, H, W, device="cuda").to(dtype)
+    patch = Cc * k * k
+    cols = C.im2col(x.reshape(-1), B, Cc, H, W, k, stride, pad, ld)
+    assert cols.shape[1] == ld
+    unf = torch.nn.functional.unfold(x.float(), k, padding=pad, stride=stride)
+    ref = unf.transpose(1, 2).reshape(-1, patch)
+    assert torch.equal(cols[:, :patch].float(), ref)
+    assert torch.all(cols[:, patch:] == 0)
+    g = torch.randn(cols.shape[0], ld, device="cuda").to(dtype)
+    din = C.col2im(g[:, :patch], B, Cc, H, W, k, stride, pad)
+    L = unf.shape[-1]
+    ref_din = torch.nn.functional.fold(g[:, :patch].float().view(B, L, patch).transpose(1, 2), (H, W), k,
+                                       padding=pad, stride=stride)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(din.view(B, Cc, H, W).float(), ref_din, **tol)
+
+
 def test_pointwise_losses(C):
     torch.manual_seed(7)
     p = torch.randn(1000, device="cuda")
@@ -538,3 +566,66 @@ print("CASE_OK")
     env = dict(os.environ, LT_GEMM_PAIR=pair)
     r = subprocess.run([sys.executable, "-c", body], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "CASE_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-2500:])
+
+
+def test_late_wait_kernels_match_serial_order():
+    """A weight-gradient GEMM marked independent of the kernel before it (it starts in that
+    kernel's tail and waits for it before exiting) gives the bits of the serial order, every
+    time, and what follows sees all of it finished."""
+    from luatorch_b200 import _backend as B
+    torch.manual_seed(21)
+    M, K, N = 4096, 768, 3072
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
+    g = torch.randn(M, N, device="cuda").bfloat16()
+    ref_dx = B.gemm(g, w, b_t=True)
+    ref_y = B.gemm(ref_dx, w)
+    ref_dw = torch.empty(K, N, device="cuda")
+    B.gemm(x, g, a_t=True, out=ref_dw)
+    ref_db = torch.empty(N, device="cuda")
+    B.column_sum(g, ref_db, False)
+    torch.testing.assert_close(ref_dw, x.float().t() @ g.float(), atol=0.5, rtol=2e-2)
+    torch.testing.assert_close(ref_db, g.float().sum(0), atol=1e-2, rtol=1e-3)
+    for it in range(12):
+        dw = torch.full((K, N), float("nan"), device="cuda")
+        db = torch.full((N,), float("nan"), device="cuda")
+        dx = B.gemm(g, w, b_t=True)
+        B.gemm(x, g, a_t=True, out=dw, overlap_prev=1)
+        B.column_sum(g, db, False)
+        y = B.gemm(dx, w)                                  # a consumer right behind the chain
+        assert torch.equal(dx, ref_dx) and torch.equal(dw, ref_dw) and torch.equal(db, ref_db), it
+        assert torch.equal(y, ref_y), it
+
+
+@pytest.mark.parametrize("M,N,K,bias,out_dtype,acc,two", [
+    (32, 27, 131072, False, torch.float32, True, True),   # conv weight gradient: odd N, very long K
+    (128, 10, 8192, True, torch.bfloat16, False, True),   # classifier head: bias added by the reduction
+    (64, 288, 32768, False, torch.float32, False, False),
+])
+def test_gemm_split_k_any_width_and_bias(M, N, K, bias, out_dtype, acc, two):
+    """Long-K products with a single output tile are cut along K whatever the output width:
+    workspace rows are padded to four floats and the closing pass adds the bias."""
+    from luatorch_b200 import _backend as B
+    torch.manual_seed(22)
+    a = (torch.randn(K, M, device="cuda") * 0.1).bfloat16()        # stored [K, M]: a_t
+    ldb = (N + 7) // 8 * 8
+    bfull = torch.zeros(K, ldb, device="cuda", dtype=torch.bfloat16)
+    bfull[:, :N] = (torch.randn(K, N, device="cuda") * 0.1).bfloat16()
+    b = bfull[:, :N]
+    bv = torch.randn(N, device="cuda").bfloat16() if bias else None
+    ldc = (N + 7) // 8 * 8 if out_dtype == torch.bfloat16 else N
+    out_full = torch.full((M, ldc), 0.25, device="cuda", dtype=out_dtype)
+    out = out_full[:, :N]
+    before = sum(lf_launches())
+    B.gemm(a, b, a_t=True, out=out, accumulate=acc, bias=bv, n_valid=N)
+    if two:
+        assert sum(lf_launches()) - before == 2        # sliced product + closing pass
+    ref = a.float().t() @ b.float()
+    if bias:
+        ref = ref + bv.float()
+    if acc:
+        ref = ref + 0.25
+    tol = dict(atol=2e-2, rtol=2e-3) if out_dtype == torch.float32 else dict(atol=0.15, rtol=2e-2)
+    torch.testing.assert_close(out.float(), ref, **tol)
+    if ldc > N:
+        assert torch.all(out_full[:, N:] == 0.25)      # nothing written beyond the logical width
