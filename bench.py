@@ -12,12 +12,15 @@ AdamW lr 6e-4 wd 0.1, bf16 compute with fp32 master weights; synthetic uniform t
 random-init weights.  Weak scaling: per-GPU work is fixed.
 
 The step runs through the public API; by default it is captured once into a CUDA graph
-(`lf.cuda.GraphedStep`: forward, loss, backward, the per-bucket fused reduce + AdamW kernels) and
-replayed, `--graph 0` launches it eagerly.  Two timed regions of K steps each, both bracketed
-by barrier + synchronize and timed with CUDA events on the launching stream:
+(`lf.cuda.GraphedStep`: input/target slicing, forward, loss, backward, the per-bucket fused
+reduce + AdamW kernels) and replayed, `--graph 0` launches it eagerly.  Two timed regions of K
+steps each, both bracketed by barrier + synchronize and timed with CUDA events on the
+launching stream:
   value      steps fed from device-resident token batches (kernel-side throughput)
-  e2e.value  steps through the same public API with every step's tokens copied from pinned
-             host memory and the loss read back to the host
+  e2e.value  steps through the same public API with every step's [B, S+1] tokens copied from
+             pinned host memory (straight into the graph's static input) and every step's
+             loss copied back to the host; the host reads each loss one step behind
+             (`lf.cuda.ScalarFetcher`), so it never waits on the step it has just launched
 Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
@@ -85,13 +88,12 @@ def run_ours(args):
     n_pool = 8
     host_tokens = [torch.randint(0, cfg["vocab"], (B, S + 1), generator=gen, dtype=torch.int32).pin_memory()
                    for _ in range(n_pool)]
-    dev_batches = []
-    for t in host_tokens:
-        d = t.cuda()
-        dev_batches.append((lf.Tensor.wrap(d[:, :-1].contiguous()),
-                            lf.Tensor.wrap(d[:, 1:].contiguous().reshape(-1))))
+    dev_batches = [lf.Tensor.wrap(t.cuda()) for t in host_tokens]
 
-    def train_step(x, y):
+    def train_step(tok):
+        """One step on a [B, S+1] int32 token batch that is already on the device."""
+        x = lf.Tensor.wrap(tok._t[:, :-1].contiguous())
+        y = lf.Tensor.wrap(tok._t[:, 1:].contiguous().reshape(-1))
         lf.autograd.zero_graph()
         ddp.zero_grad()
         loss = crit(ddp(x), y)
@@ -104,11 +106,10 @@ def run_ours(args):
     kernels_per_replay = 0
     if args.graph:
         # the public whole-step replay: static input tensors, one graph launch per step
-        gx = lf.Tensor.wrap(dev_batches[0][0]._t.clone())
-        gy = lf.Tensor.wrap(dev_batches[0][1]._t.clone())
+        gtok = lf.Tensor.wrap(dev_batches[0]._t.clone())
         c_before = sum(lf.launch_counts())
         try:
-            runner = lf.cuda.GraphedStep(lambda: train_step(gx, gy), opt, inputs=(gx, gy), warmup=2,
+            runner = lf.cuda.GraphedStep(lambda: train_step(gtok), opt, inputs=(gtok,), warmup=2,
                                          pdl=True)
         except Exception as e:      # capture refused on this machine: every rank goes eager
             print("bench: graph capture failed (%r), running eagerly" % (e,), file=sys.stderr)
@@ -123,16 +124,22 @@ def run_ours(args):
         kernels_per_replay = (sum(lf.launch_counts()) - c_before) // 3 if runner is not None else 0
 
     def step_resident(i):
-        x, y = dev_batches[i % n_pool]
-        return runner(x, y) if runner is not None else train_step(x, y)
+        tok = dev_batches[i % n_pool]
+        return runner(tok) if runner is not None else train_step(tok)
+
+    fetch = lf.cuda.ScalarFetcher(depth=1)
+    losses = []
 
     def step_e2e(i):
-        t = host_tokens[i % n_pool]
-        d = t.to("cuda", non_blocking=True)          # H2D from pinned memory, every step
-        x = lf.Tensor.wrap(d[:, :-1].contiguous())
-        y = lf.Tensor.wrap(d[:, 1:].contiguous().reshape(-1))
-        loss = runner(x, y) if runner is not None else train_step(x, y)
-        return loss.item()                            # D2H read of the loss, every step
+        t = host_tokens[i % n_pool]                   # pinned host memory
+        if runner is not None:
+            loss = runner(t)                          # H2D straight into the graph's static input
+        else:
+            loss = train_step(lf.Tensor.wrap(t.to("cuda", non_blocking=True)))
+        v = fetch.push(loss)                          # D2H copy of this step's loss, every step;
+        if v is not None:                             # the host reads the previous step's value
+            losses.append(v)
+        return v
 
     def sync_all():
         torch.cuda.synchronize()
@@ -148,6 +155,7 @@ def run_ours(args):
         last = None
         for i in range(steps):
             last = fn(i)
+        losses.extend(fetch.drain())      # the last steps' losses reach the host inside the region
         e1.record()
         sync_all()
         ms = e0.elapsed_time(e1)
@@ -160,12 +168,21 @@ def run_ours(args):
     for i in range(warmup):
         step_resident(i)
     ddp.check()
+    # clocks are sampled per region: the second region starts once the power limiter has settled
+    # (a B200 under its 1 kW cap runs the first few hundred milliseconds of a burst faster), so
+    # the two numbers differ by that as well as by the copies
     sampler = ClockSampler(dev, 0.025).start()
     ms_dev, launches, last_loss = timed(step_resident, args.steps)
+    clocks = sampler.stop()
     for i in range(2):
         step_e2e(i)
-    ms_e2e, _, loss_val = timed(step_e2e, args.steps)
-    clocks = sampler.stop()
+    fetch.drain()
+    losses.clear()
+    sampler = ClockSampler(dev, 0.025).start()
+    ms_e2e, _, _ = timed(step_e2e, args.steps)
+    clocks_e2e = sampler.stop()
+    assert len(losses) == args.steps, (len(losses), args.steps)   # one host-side loss per step
+    loss_val = losses[-1]
     ddp.check()
 
     tokens_per_step = B * S * world
@@ -188,7 +205,7 @@ def run_ours(args):
                        "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2)},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 4, "d2h_bytes_per_step": 4,
-                    "final_loss": loss_val},
+                    "final_loss": loss_val, "clocks": clocks_e2e},
             # host launches counted in the timed region, plus the kernels each graph replay runs
             "gpu_launches": int(launches + kernels_per_replay * args.steps),
             "clocks": clocks,

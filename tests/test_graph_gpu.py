@@ -184,3 +184,21 @@ def test_graphed_step_with_ddp_wrapper_and_sgd():
         last_g = graphed().item()
     assert abs(last_g - last_e) <= 1e-5 * max(1.0, abs(last_e)), (last_g, last_e)
     torch.testing.assert_close(ddp_g.arena.master, ddp_e.arena.master, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_scalar_fetcher_reads_device_scalars_one_step_behind():
+    """Every pushed device scalar reaches the host, in order, through pinned memory, and the
+    value handed back by push() is the one queued `depth` calls earlier."""
+    import luatorch_b200 as lf
+    f = lf.cuda.ScalarFetcher(depth=1)
+    src = torch.arange(16, device="cuda", dtype=torch.float32) * 0.5
+    buf = torch.zeros(1, device="cuda")
+    got = []
+    for i in range(16):
+        buf.copy_(src[i:i + 1])            # the same static buffer every time, as a graph's output
+        v = f.push(lf.Tensor.wrap(buf))
+        if v is not None:
+            got.append(v)
+    got += f.drain()
+    assert got == [0.5 * i for i in range(16)]

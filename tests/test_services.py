@@ -301,3 +301,15 @@ def test_nvtx_ranges_and_comm_fields_in_the_logger(tmp_path, capsys):
     recs = [json.loads(l) for l in open(path)]
     assert recs[0]["comm"]["buckets_ms"] == [0.1, 0.25] and recs[0]["comm"]["pool"]["allocated_mb"] == 12.0
     assert recs[1]["tokens_per_s"] == 50000.0
+
+
+def test_scalar_fetcher_returns_values_one_call_behind():
+    """CPU fallback of the one-step-behind loss reader: same order, nothing lost."""
+    import luatorch_b200 as lf
+    f = lf.cuda.ScalarFetcher(depth=2)
+    got = [f.push(torch.tensor([float(i)])) for i in range(5)]
+    assert got == [None, None, 0.0, 1.0, 2.0]
+    assert f.drain() == [3.0, 4.0]
+    assert f.drain() == []
+    f0 = lf.cuda.ScalarFetcher(depth=0)
+    assert f0.push(lf.Tensor.wrap(torch.tensor([7.5]))) == 7.5
