@@ -2,7 +2,7 @@
 // CTA, operands staged in shared memory by TMA (128-byte swizzle), fp32 accumulators
 // in TMEM, epilogue read back with tcgen05.ld.
 //
-// Structure: persistent kernels, one CTA per SM, 64 + 32 * EPI_WARPS (= 320) threads:
+// Structure: persistent kernels, one CTA per SM, 64 + 32 * EPI_WARPS (= 576) threads:
 //   warp 0       TMA producer (one lane issues the tiled loads of each pipeline stage)
 //   warp 1       TMEM owner + MMA issuer (one lane)
 //   warps 2..9   epilogue: two warps per 32-lane TMEM quadrant of the 128-row tile, each
@@ -44,8 +44,12 @@ constexpr int BM = 128;
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+// Sixteen epilogue warps (four per scheduler): with K = 768 a 256-wide tile's main loop lasts
+// about 6000 cycles and a GELU / dGELU epilogue of 128 x 256 outputs per CTA needs that many
+// issue slots, so with eight warps (two per scheduler, low IPC) the epilogue was the longer
+// side of the pipeline: measured 58.9 -> 50.1 us for [8192,768]x[768,3072]^T with dGELU.
 #ifndef LT_EPI_WARPS
-#define LT_EPI_WARPS 8
+#define LT_EPI_WARPS 16
 #endif
 constexpr int EPI_WARPS = LT_EPI_WARPS;     // EPI_WARPS/4 warps per TMEM lane quadrant share the columns
 constexpr int EPI_SPLIT = EPI_WARPS / 4;
@@ -216,23 +220,19 @@ __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float* v,
 }
 
 // Epilogue of one 128 x BN accumulator tile: this warp's 32 rows (TMEM lane quadrant `quad`)
-// and column slice `half` of EPI_SPLIT, read from TMEM address `t_row`, written to C.
+// and every EPI_SPLIT-th 32-column chunk starting at chunk `half`, read from TMEM address
+// `t_row`, written to C.  (Round robin: BN = 192 gives two of the four warps of a quadrant two
+// chunks and the others one; BN = 64 leaves two of them idle.)
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_row, int m0, int n0,
                                               int bi, int bo, int quad, int half, int lane) {
-  constexpr int HALF_COLS = BN / EPI_SPLIT;
-#ifndef LT_EPI_CW
-#define LT_EPI_CW 64
-#endif
-  constexpr int EPI_CW = (HALF_COLS % LT_EPI_CW == 0) ? LT_EPI_CW : 32;
+  constexpr int EPI_CW = 32;
   const long long row = m0 + quad * 32 + lane;
   const bool row_ok = row < p.M;
   const size_t esz = p.c_fp32 ? 4 : 2;
   char* c_base = (char*)p.C + (size_t)(bi * p.c_stride_inner + bo * p.c_stride_outer) * esz;
-  // TMEM is read in batches of EPI_CW columns: all loads of a batch are issued before the
-  // single wait, so their latencies overlap instead of adding up.
 #pragma unroll 1
-  for (int cb = half * HALF_COLS; cb < (half + 1) * HALF_COLS; cb += EPI_CW) {
+  for (int cb = half * EPI_CW; cb < BN; cb += EPI_CW * EPI_SPLIT) {
     if (n0 + cb >= p.N) break;  // uniform across the warp
     uint32_t rr[EPI_CW];
 #pragma unroll
@@ -912,7 +912,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         quad, half, lane);
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+      // relaxed: the barrier only hands the accumulator columns back, and this warp's TMEM
+      // reads are complete (tcgen05.wait::ld, tcgen05 fence above); a release at cluster scope
+      // would first wait for the tile's global stores to reach L2 (2-3 us per launch)
+      if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (p.g_world > 1 && p.g_done && (int)threadIdx.x - 64 < p.g_world) {
