@@ -95,7 +95,8 @@ struct KernelParams {
   int causal_tiles;
   int causal_k;
   int vec_ok;  // C / residual / aux rows allow 16-byte vector access
-  int vec32_ok;  // ... and 32-byte (256-bit) access
+  int vec32_ok;  // ... and 32-byte (256-bit) access (bf16 output, residual, aux)
+  int c32_ok;    // fp32 output rows allow 32-byte access
   // all-gather of B fused into the kernel (g_world <= 1: off)
   const uint64_t* g_b_ptrs;
   const uint64_t* g_signal_ptrs;
@@ -303,15 +304,41 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
         for (int i = 0; i < 32; ++i) v[i] += x[i];
       }
       if (p.c_fp32) {
-        float4* cp = reinterpret_cast<float4*>((float*)c_base + row * p.ldc + col0);
+        float* cf = (float*)c_base + row * p.ldc + col0;
+        if (p.c32_ok) {
+          // 128 bytes per lane as four 256-bit accesses (the epilogue's cost follows the number
+          // of 32-byte sectors an instruction touches: 16-byte accesses write each sector twice)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          if (p.accumulate) {
-            float4 old = cp[i];
-            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          for (int i = 0; i < 4; ++i) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = v[8 * i + j];
+            if (p.accumulate) {
+              float q[8];
+              asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                           : "=f"(q[0]), "=f"(q[1]), "=f"(q[2]), "=f"(q[3]), "=f"(q[4]), "=f"(q[5]),
+                             "=f"(q[6]), "=f"(q[7])
+                           : "l"(cf + 8 * i)
+                           : "memory");
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] += q[j];
+            }
+            asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(cf + 8 * i),
+                         "f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3]), "f"(o[4]), "f"(o[5]), "f"(o[6]),
+                         "f"(o[7])
+                         : "memory");
           }
-          cp[i] = o;
+        } else {
+          float4* cp = reinterpret_cast<float4*>(cf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            if (p.accumulate) {
+              float4 old = cp[i];
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            cp[i] = o;
+          }
         }
       } else {
         __nv_bfloat16* cp = (__nv_bfloat16*)c_base + row * p.ldc + col0;
@@ -1076,6 +1103,8 @@ KernelParams make_params(const GemmArgs& a) {
   if (a.aux_out) w = w && a32(a.aux_out);
   if (a.aux_in) w = w && a32(a.aux_in) && a.ld_aux % 16 == 0;
   p.vec32_ok = w ? 1 : 0;
+  p.c32_ok = (v && a.c_fp32 && a32(a.C) && a.ldc % 8 == 0 && a.c_stride_inner % 8 == 0 &&
+              a.c_stride_outer % 8 == 0) ? 1 : 0;
   p.late_wait = 0;   // set by the launcher (launch_late)
   p.g_b_ptrs = nullptr; p.g_signal_ptrs = nullptr; p.g_flags = nullptr; p.g_status = nullptr;
   p.g_ldb = 0; p.g_rank = 0; p.g_world = 1; p.g_rows_per_shard = 0; p.g_done = 0; p.g_epoch = 0;
