@@ -423,6 +423,29 @@ std::vector<Tensor> layernorm_forward(const Tensor& x, const Tensor& gamma, cons
         "layernorm_forward");
   return {y, mean, rstd};
 }
+// Partial rows of the LayerNorm backward: one buffer per device that lives outside the
+// caching allocator's reuse (allocated once, grown when a larger one is asked for, never
+// while a graph is being captured).  `*is_private` tells the launcher whether it got it.
+Tensor ln_scratch(int64_t n, const Tensor& like, int* is_private) {
+  static std::mutex mu;
+  static std::map<int, Tensor> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  const int dev = like.get_device();
+  auto it = cache.find(dev);
+  if (it == cache.end() || it->second.numel() < n) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(cur_stream(), &st);
+    if (st != cudaStreamCaptureStatusNone) {
+      *is_private = 0;
+      return scratch_floats(n, like);
+    }
+    if (it != cache.end()) cache.erase(it);
+    it = cache.emplace(dev, at::empty({n}, like.options().dtype(at::kFloat))).first;
+  }
+  *is_private = 1;
+  return it->second;
+}
+
 // returns dx; dgamma / dbeta are written (or accumulated) into the given buffers
 Tensor layernorm_backward(const Tensor& x, const Tensor& dy, const Tensor& gamma,
                           const Tensor& mean, const Tensor& rstd, const OptT& dx_add,
@@ -432,11 +455,13 @@ Tensor layernorm_backward(const Tensor& x, const Tensor& dy, const Tensor& gamma
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t cols = x.size(-1), rows = x.numel() / cols;
   Tensor dx = at::empty_like(x);
-  Tensor scratch = scratch_floats(lt::layernorm_backward_scratch_floats(rows, cols), x);
+  int priv = 0;
+  Tensor scratch = ln_scratch(lt::layernorm_backward_scratch_floats(rows, cols), x, &priv);
   check(lt::layernorm_backward(dt(x), x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), dt(gamma),
                                mean.data_ptr<float>(), rstd.data_ptr<float>(), optptr(dx_add),
                                dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), dt(dgamma),
-                               accumulate, scratch.data_ptr<float>(), rows, cols, cur_stream()),
+                               accumulate, scratch.data_ptr<float>(), rows, cols, cur_stream(),
+                               nullptr, 0, nullptr, priv),
         "layernorm_backward");
   return dx;
 }
@@ -453,13 +478,14 @@ std::tuple<Tensor, bool> layernorm_backward_dxsum(const Tensor& x, const Tensor&
   const int64_t cols = x.size(-1), rows = x.numel() / cols;
   TORCH_CHECK(dxsum.numel() == cols && dxsum.is_contiguous());
   Tensor dx = at::empty_like(x);
-  Tensor scratch = scratch_floats(lt::layernorm_backward_scratch_floats(rows, cols), x);
+  int priv = 0;
+  Tensor scratch = ln_scratch(lt::layernorm_backward_scratch_floats(rows, cols), x, &priv);
   int done = 0;
   check(lt::layernorm_backward(dt(x), x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), dt(gamma),
                                mean.data_ptr<float>(), rstd.data_ptr<float>(), optptr(dx_add),
                                dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), dt(dgamma),
                                accumulate, scratch.data_ptr<float>(), rows, cols, cur_stream(),
-                               dxsum.data_ptr(), dxsum_accumulate ? 1 : 0, &done),
+                               dxsum.data_ptr(), dxsum_accumulate ? 1 : 0, &done, priv),
         "layernorm_backward");
   return {dx, done != 0};
 }

@@ -67,20 +67,40 @@ inline bool late_wait_enabled() {
   return v != 0 && pdl_enabled();
 }
 
-// Number of late-wait kernels launched back to back just before now (0 after any other launch
-// through launch_pdl).  A late-wait kernel triggers without having waited, so the kernel after
-// it can start while the one before it still runs: a kernel may therefore ask for late wait
-// only if it is independent of the previous `independent_of` launches and the chain of late
-// kernels in front of it is shorter than that.  late_wait_begin() decides, the caller launches
-// (which resets the chain) and calls late_wait_commit() when the launch was a late one.
-extern int g_late_chain;
-struct LateWait { int on, chain; };
+// Bookkeeping for late wait.  A late kernel triggers without having waited, so the kernel after
+// it can start while the ones before it still run.  When a kernel K is about to be launched,
+// the launches in front of it look like   ... N [S] C1 .. Cc   where N is a normal kernel (it
+// waited, then triggered), S an optional side kernel (below) and C1..Cc the late kernels
+// launched back to back just before now.  When K runs, everything before N is complete; N
+// (or S, which waited for N) and C1..Cc may still be running.  K may therefore be late only
+// if it is independent of C1..Cc and of N: its caller vouches for the `independent_of`
+// launches in front of it, and that number must cover them.  late_wait_begin() decides, the
+// caller launches (launch_pdl resets the chain) and calls late_wait_commit().
+//
+// Side kernels.  A kernel whose only outputs are parameter gradients (the LayerNorm parameter
+// reduction) is a dead end of the stream's data flow until the optimizer runs: its launcher
+// calls mark_side_kernel() right after it.  Every later kernel is independent of it by
+// construction, so it does not count: in  N S C1 .. Cc  the kernel K needs to vouch for c
+// launches only (S waited for N, so N is complete), and the first kernel behind S may be late
+// without vouching for anything.  This relies on two facts: the late-wait kernels (GEMM,
+// attention backward) never read a parameter gradient, and the side kernel's scratch is not
+// memory that the stream's allocator could hand to the next kernel (the binding keeps it in a
+// buffer of its own).
+extern int g_late_chain;       // c: late kernels launched back to back just before now
+extern int g_late_side;        // 1: that chain stands right behind a side kernel
+extern unsigned long long g_pdl_seq, g_side_mark;
+inline void mark_side_kernel() { g_side_mark = g_pdl_seq; }
+struct LateWait { int on, chain, side; };
 inline LateWait late_wait_begin(int independent_of) {
-  LateWait l{0, g_late_chain};
-  l.on = (late_wait_enabled() && independent_of > l.chain) ? 1 : 0;
+  LateWait l{0, g_late_chain, 0};
+  l.side = l.chain == 0 ? (g_side_mark != 0 && g_side_mark == g_pdl_seq) : (g_late_side != 0);
+  const int need = l.chain + (l.side ? 0 : 1);
+  l.on = (late_wait_enabled() && independent_of >= need) ? 1 : 0;
   return l;
 }
-inline void late_wait_commit(const LateWait& l) { if (l.on) g_late_chain = l.chain + 1; }
+inline void late_wait_commit(const LateWait& l) {
+  if (l.on) { g_late_chain = l.chain + 1; g_late_side = l.side; }
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -96,6 +116,8 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.attrs = &attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
   g_late_chain = 0;
+  g_late_side = 0;
+  ++g_pdl_seq;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -16,6 +16,8 @@ std::atomic<uint64_t> g_ops_launches{0};
 uint64_t ops_launch_count() { return g_ops_launches.load(); }
 int g_pdl_override = -1;
 int g_late_chain = 0;
+int g_late_side = 0;
+unsigned long long g_pdl_seq = 0, g_side_mark = 0;
 void set_pdl_override(int v) { g_pdl_override = v < 0 ? -1 : (v != 0); }
 
 namespace {

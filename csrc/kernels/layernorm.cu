@@ -688,7 +688,7 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
                                const void* dx_add, void* dx, void* dgamma, void* dbeta,
                                int grad_dtype, int accumulate, float* scratch, int64_t rows,
                                int64_t cols, cudaStream_t s, void* dxsum, int dxsum_accumulate,
-                               int* dxsum_done) {
+                               int* dxsum_done, int scratch_is_private) {
   if (dxsum_done) *dxsum_done = 0;
   if (rows <= 0 || cols <= 0) return cudaSuccess;
   int nparts = 0;
@@ -711,6 +711,9 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
                  dxsum_accumulate);
       LT_COUNT_LAUNCH();
     })
+    // dx is final before this reduction starts and nothing downstream reads what it writes:
+    // the kernel launched next may run beside it (see mark_side_kernel in common.cuh)
+    if (scratch_is_private) mark_side_kernel();
     if (dxsum_done) *dxsum_done = dxs_done ? 1 : 0;
   }
   return cudaGetLastError();

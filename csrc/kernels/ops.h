@@ -111,7 +111,11 @@ cudaError_t layernorm_backward(int dtype, const void* x, const void* dy, const v
                                const void* dx_add, void* dx, void* dgamma, void* dbeta,
                                int grad_dtype, int accumulate, float* scratch, int64_t rows,
                                int64_t cols, cudaStream_t s, void* dxsum = nullptr,
-                               int dxsum_accumulate = 0, int* dxsum_done = nullptr);
+                               int dxsum_accumulate = 0, int* dxsum_done = nullptr,
+                               int scratch_is_private = 0);
+// `scratch_is_private`: the caller owns `scratch` outside the stream's caching allocator (it
+// cannot be handed to the kernel launched next); the closing parameter reduction is then
+// marked as a side kernel, so that a following GEMM may run beside it.
 cudaError_t gelu_bias_forward(int dtype, const void* x, const void* bias, int bias_dtype,
                               void* out, int64_t rows, int64_t cols, cudaStream_t s);
 // dx = dy * gelu'(x + bias)
