@@ -56,7 +56,7 @@ class Timer:
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="", help="comma list of: gemm,attention,layernorm,softmax_ce,elementwise,adamw,embedding")
+    ap.add_argument("--only", default="", help="comma list of: gemm,gemm_epilogue,attention,layernorm,softmax_ce,elementwise,adamw,embedding")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--csv", default="")
@@ -94,6 +94,31 @@ def main(argv=None):
                        big_operands=(M * K + K * N + M * N) * 2 > 150e6)
             add("gemm", "bf16 [%d,%d]x[%d,%d] %s%s" % (M, K, K, N, "At" if a_t else "A", "B" if b_n else "Bt"), ms,
                 2.0 * M * N * K, 2.0 * (M * K + K * N + M * N))
+    if not only or "gemm_epilogue" in only:
+        # the fused epilogues of one GPT-124M MLP block against the plain product of the same shape
+        M, K, N = 8192, 768, 3072
+        x = (torch.randn(M, K, device="cuda") * 0.1).to(bf)
+        w1 = (torch.randn(K, N, device="cuda") * 0.05).to(bf)
+        w2 = (torch.randn(N, K, device="cuda") * 0.05).to(bf)
+        bias = torch.randn(N, device="cuda").to(bf)
+        out = torch.empty(M, N, device="cuda", dtype=bf)
+        pre = torch.empty_like(out)
+        res = torch.randn(M, K, device="cuda").to(bf)
+        out_k = torch.empty(M, K, device="cuda", dtype=bf)
+        fl = 2.0 * M * N * K
+        nb_ops = 2.0 * (M * K + K * N)
+        nb_out = 2.0 * M * N
+        for name, fn, nbytes in [
+            ("[8192,768]x[768,3072] plain", lambda: B.gemm(x, w1, out=out), nb_ops + nb_out),
+            ("  + bias", lambda: B.gemm(x, w1, bias=bias, out=out), nb_ops + nb_out),
+            ("  + bias + GELU + pre-activation out", lambda: B.gemm(x, w1, bias=bias, act=1, aux_out=pre, out=out), nb_ops + 2 * nb_out),
+            ("[8192,768]x[3072,768]^T plain (dgrad)", lambda: B.gemm(x, w2, b_t=True, out=out), nb_ops + nb_out),
+            ("  * GELU'(pre-activation in)", lambda: B.gemm(x, w2, b_t=True, act=2, aux_in=pre, out=out), nb_ops + 2 * nb_out),
+            ("[8192,3072]x[3072,768] plain", lambda: B.gemm(out, w2, out=out_k), 2.0 * (M * N + N * K + M * K)),
+            ("  + bias + residual", lambda: B.gemm(out, w2, bias=bias[:K].contiguous(), residual=res, out=out_k),
+             2.0 * (M * N + N * K + 2 * M * K)),
+        ]:
+            add("gemm_epi", name, timer(fn), fl, nbytes)
     if not only or "attention" in only:
         for Bn, S, H, D in [(8, 1024, 12, 64), (4, 2048, 16, 128)]:
             qkv = (torch.randn(Bn, S, 3, H, D, device="cuda") * 0.5).to(bf)
