@@ -124,6 +124,34 @@ __device__ __forceinline__ float dgelu_f(float x) {
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k0 * (1.0f + 3.0f * k1 * x * x);
 }
 
+// The same two functions on a pair of values with packed f32x2 arithmetic (one instruction
+// per two elements; the tanh stays one MUFU each).  The epilogue of a K = 768 product is bound
+// by instruction issue, so the vector path uses these.
+//   gelu(x)  = h + h t,                  h = x / 2, t = tanh(x (k0 + k0 k1 x^2))
+//   gelu'(x) = s + s r (1 - s) 2,        s = (1 + t) / 2, r = x (k0 + 3 k0 k1 x^2)
+__device__ __forceinline__ float2 tanh_arg2(float2 x, float2 x2) {
+  const float k0 = 0.7978845608f, k0k1 = 0.7978845608f * 0.044715f;
+  return fmul2(x, ffma2(x2, make_float2(k0k1, k0k1), make_float2(k0, k0)));
+}
+__device__ __forceinline__ float2 gelu2(float2 x) {
+  const float2 u = tanh_arg2(x, fmul2(x, x));
+  const float2 t = make_float2(tanh_fast(u.x), tanh_fast(u.y));
+  const float2 h = fmul2(x, make_float2(0.5f, 0.5f));
+  return ffma2(h, t, h);
+}
+// returns v * gelu'(x)
+__device__ __forceinline__ float2 dgelu_mul2(float2 v, float2 x) {
+  const float k0 = 0.7978845608f, k0k1 = 0.7978845608f * 0.044715f;
+  const float2 x2 = fmul2(x, x);
+  const float2 u = tanh_arg2(x, x2);
+  const float2 t = make_float2(tanh_fast(u.x), tanh_fast(u.y));
+  const float2 s = ffma2(t, make_float2(0.5f, 0.5f), make_float2(0.5f, 0.5f));
+  // r2 = 2 x (k0 + 3 k0 k1 x^2)
+  const float2 r2 = fmul2(x, ffma2(x2, make_float2(6.0f * k0k1, 6.0f * k0k1), make_float2(2.0f * k0, 2.0f * k0)));
+  const float2 z = ffma2(fmul2(r2, s), make_float2(-1.0f, -1.0f), r2);      // r2 (1 - s)
+  return fmul2(v, ffma2(s, z, s));
+}
+
 // Scalar epilogue for one element, shared by the tensor-core tail path and the SIMT
 // fallback kernel.
 __device__ __forceinline__ void epilogue_store_scalar(const KernelParams& p, char* c_base,
@@ -260,8 +288,10 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
           const float4* bp = reinterpret_cast<const float4*>((const float*)p.bias + col0);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            float4 bv = __ldg(bp + i);
-            v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
+            const float4 bv = __ldg(bp + i);
+            const float2 s0 = fadd2(make_float2(v[4 * i], v[4 * i + 1]), make_float2(bv.x, bv.y));
+            const float2 s1 = fadd2(make_float2(v[4 * i + 2], v[4 * i + 3]), make_float2(bv.z, bv.w));
+            v[4 * i] = s0.x; v[4 * i + 1] = s0.y; v[4 * i + 2] = s1.x; v[4 * i + 3] = s1.y;
           }
         } else {
           const uint4* bp =
@@ -271,7 +301,10 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
             float f[8];
             unpack8(__ldg(bp + i), f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[8 * i + j] += f[j];
+            for (int j = 0; j < 8; j += 2) {
+              const float2 sj = fadd2(make_float2(v[8 * i + j], v[8 * i + j + 1]), make_float2(f[j], f[j + 1]));
+              v[8 * i + j] = sj.x; v[8 * i + j + 1] = sj.y;
+            }
           }
         }
       }
@@ -281,7 +314,10 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
         }
         if (p.act == GEMM_ACT_GELU) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
+          for (int i = 0; i < 32; i += 2) {
+            const float2 g = gelu2(make_float2(v[i], v[i + 1]));
+            v[i] = g.x; v[i + 1] = g.y;
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
@@ -291,7 +327,10 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
         load_bf16x32(p.aux_in + row * p.ld_aux + col0, x, p.vec32_ok);
         if (p.act == GEMM_ACT_DGELU) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= dgelu_f(x[i]);
+          for (int i = 0; i < 32; i += 2) {
+            const float2 g = dgelu_mul2(make_float2(v[i], v[i + 1]), make_float2(x[i], x[i + 1]));
+            v[i] = g.x; v[i + 1] = g.y;
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = x[i] > 0.0f ? v[i] : 0.0f;
@@ -301,7 +340,10 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, uint32_t t_
         float x[32];
         load_bf16x32(p.residual + row * p.ldr + col0, x, p.vec32_ok);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] += x[i];
+        for (int i = 0; i < 32; i += 2) {
+          const float2 si = fadd2(make_float2(v[i], v[i + 1]), make_float2(x[i], x[i + 1]));
+          v[i] = si.x; v[i + 1] = si.y;
+        }
       }
       if (p.c_fp32) {
         float* cf = (float*)c_base + row * p.ldc + col0;
