@@ -82,6 +82,9 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, int64_t M, int64_t N, int
           int64_t c_si, int64_t c_so, double alpha, bool accumulate, const OptT& bias,
           int64_t act, const OptT& residual, int64_t ldr, const OptT& aux_out,
           const OptT& aux_in, int64_t ld_aux, int64_t causal_tiles) {
+  // the hint is for THIS call only: taken before anything can throw
+  const int overlap_prev = g_next_gemm_overlap;
+  g_next_gemm_overlap = 0;
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm operands must be CUDA tensors");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
               "gemm operands must be bfloat16");
@@ -114,8 +117,7 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, int64_t M, int64_t N, int
   if (aux_out.has_value()) g.aux_out = aux_out->data_ptr();
   if (aux_in.has_value()) { g.aux_in = aux_in->data_ptr(); g.ld_aux = ld_aux; }
   g.causal_tiles = (int)causal_tiles;
-  g.overlap_prev = g_next_gemm_overlap;
-  g_next_gemm_overlap = 0;
+  g.overlap_prev = overlap_prev;
   // scratch for split-K comes from torch's caching allocator, so it is stream-ordered
   Tensor ws;
   const size_t ws_bytes = lt::gemm_split_k_workspace_bytes(g);
