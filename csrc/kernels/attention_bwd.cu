@@ -814,6 +814,15 @@ cudaError_t launch_bwd2(const CUtensorMap& f0, const CUtensorMap& f1, const CUte
   return cudaGetLastError();
 }
 
+// LT_FLASH_BWD2_D128=1: the second-generation kernels at head dim 128 as well (one CTA per SM)
+bool use_bwd2_d128() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LT_FLASH_BWD2_D128");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v != 0;
+}
 // LT_FLASH_BWD_V1=1 keeps the first-generation kernels (comparison runs)
 bool use_bwd_v1() {
   static int v = -1;
@@ -861,7 +870,7 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
   if (de != cudaSuccess) return de;
   g_attn_launches.fetch_add(1, std::memory_order_relaxed);
 
-  if (a.D == 64 && a.S % BT == 0 && !use_bwd_v1() &&
+  if ((a.D == 64 || (a.D == 128 && use_bwd2_d128())) && a.S % BT == 0 && !use_bwd_v1() &&
       ((reinterpret_cast<uintptr_t>(a.lse) | reinterpret_cast<uintptr_t>(g.delta)) & 15) == 0) {
     // second-generation kernels: P / dS stay in tensor memory, two CTAs per SM
     CUtensorMap q128, k128, v128, do128, q64, k64, v64, do64;
@@ -881,13 +890,15 @@ cudaError_t flash_attention_backward(const AttnArgs& a, const AttnBwdArgs& g, cu
     dim3 grid2(a.H, a.B, a.S / BT);   // tile index slowest: longest CTAs of every head go first
     p2.out0 = (__nv_bfloat16*)g.dk; p2.o0_sb = g.dk_sb; p2.o0_ss = g.dk_ss; p2.o0_sh = g.dk_sh;
     p2.out1 = (__nv_bfloat16*)g.dv; p2.o1_sb = g.dv_sb; p2.o1_ss = g.dv_ss; p2.o1_sh = g.dv_sh;
-    cudaError_t e2 = launch_bwd2<64, true>(k128, v128, q64, do64, p2, grid2, stream);
+    cudaError_t e2 = a.D == 64 ? launch_bwd2<64, true>(k128, v128, q64, do64, p2, grid2, stream)
+                               : launch_bwd2<128, true>(k128, v128, q64, do64, p2, grid2, stream);
     if (e2 != cudaSuccess) return e2;
     p2.out0 = (__nv_bfloat16*)g.dq; p2.o0_sb = g.dq_sb; p2.o0_ss = g.dq_ss; p2.o0_sh = g.dq_sh;
     p2.out1 = nullptr; p2.o1_sb = p2.o1_ss = p2.o1_sh = 0;
     const LateWait lw = late_wait_begin(1);   // independent of the dK / dV kernel: runs in its tail
     p2.late_wait = lw.on;
-    e2 = launch_bwd2<64, false>(q128, do128, k64, v64, p2, grid2, stream);
+    e2 = a.D == 64 ? launch_bwd2<64, false>(q128, do128, k64, v64, p2, grid2, stream)
+                   : launch_bwd2<128, false>(q128, do128, k64, v64, p2, grid2, stream);
     late_wait_commit(lw);
     return e2;
   }

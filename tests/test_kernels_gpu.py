@@ -629,3 +629,36 @@ def test_gemm_split_k_any_width_and_bias(M, N, K, bias, out_dtype, acc, two):
     torch.testing.assert_close(out.float(), ref, **tol)
     if ldc > N:
         assert torch.all(out_full[:, N:] == 0.25)      # nothing written beyond the logical width
+
+
+def test_flash_backward_second_generation_at_head_dim_128():
+    """LT_FLASH_BWD2_D128=1 runs the tensor-memory-operand backward (the default at head dim 64)
+    at head dim 128 too; the switch is read once per process, so it runs in its own.  Gradients
+    against fp32 attention."""
+    import subprocess, sys, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    body = r'''
+import sys, math, torch
+sys.path.insert(0, %r)
+from luatorch_b200 import _C
+torch.manual_seed(33)
+B, S, H, D = 2, 512, 3, 128
+qkv = (torch.randn(B, S, 3, H, D, device="cuda") * 0.5).bfloat16()
+q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+sc = 1.0 / math.sqrt(D)
+o, lse = _C.flash_forward(q, k, v, True, sc)
+d_o = (torch.randn_like(o.float()) * 0.5).bfloat16()
+dq, dk, dv = _C.flash_backward(q, k, v, o, lse, d_o, True, sc, None)[:3]
+qf, kf, vf = (t.float().permute(0, 2, 1, 3).requires_grad_(True) for t in (q, k, v))
+s = qf @ kf.transpose(-1, -2) * sc
+s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device="cuda"), 1), float("-inf"))
+ref = torch.softmax(s, -1) @ vf
+ref.backward(d_o.float().permute(0, 2, 1, 3))
+for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+    err = (got.float().permute(0, 2, 1, 3) - want).abs().max().item()
+    assert err < 0.06 * max(1.0, want.abs().max().item()), (name, err)
+print("BWD2_D128_OK")
+''' % root
+    env = dict(os.environ, LT_FLASH_BWD2_D128="1")
+    r = subprocess.run([sys.executable, "-c", body], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "BWD2_D128_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])
