@@ -262,7 +262,9 @@ constexpr int FB_MAX_BLOCKS = 3 * 148;
 // all of a warp's rows; at the end the CTA's four warps are added in a fixed binary tree
 // through shared memory (1->0 and 3->2, then 2->0) and warp 0 writes the CTA's partial row to
 // scratch.
-template <typename T, typename TP, int NV, bool DXS>
+// FULL: the row is exactly NV x 32 vectors long (cols == NV * 32 * V), so no lane ever falls
+// off its end and the bounds tests disappear (768 columns of bf16: NV = 3).
+template <typename T, typename TP, int NV, bool DXS, bool FULL>
 __global__ void __launch_bounds__(FB_THREADS, (DXS && NV >= 3) ? 2 : 3)
 ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP* __restrict__ gamma,
                     const float* __restrict__ mean, const float* __restrict__ rstd,
@@ -293,7 +295,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
-      if (vi < nvec) {
+      if (FULL || vi < nvec) {
         xraw[i] = VecIO<T>::load_raw(x + row * cols + vi * V);
         graw[i] = VecIO<T>::load_raw(dy + row * cols + vi * V);
       }
@@ -310,7 +312,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         const int64_t vi = lane + 32 * i;
-        if (vi < nvec) {
+        if (FULL || vi < nvec) {
           nx[i] = VecIO<T>::load_raw(x + nrow * cols + vi * V);
           ng[i] = VecIO<T>::load_raw(dy + nrow * cols + vi * V);
         }
@@ -324,7 +326,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         const int64_t vi = lane + 32 * i;
-        if (vi < nvec) araw[i] = VecIO<T>::load_raw(dx_add + row * cols + vi * V);
+        if (FULL || vi < nvec) araw[i] = VecIO<T>::load_raw(dx_add + row * cols + vi * V);
       }
     }
     float c1 = 0.0f, c2 = 0.0f;
@@ -332,7 +334,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
-      if (vi < nvec) {
+      if (FULL || vi < nvec) {
         float xv[V], g[V], ga[V];
         VecIO<T>::unpack(xraw[i], xv);
         VecIO<T>::unpack(graw[i], g);
@@ -354,7 +356,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int64_t vi = lane + 32 * i;
-      if (vi < nvec) {
+      if (FULL || vi < nvec) {
         float o[V], xv[V], g[V], ga[V];
         if (dx_add) VecIO<T>::unpack(araw[i], o);
         VecIO<T>::unpack(xraw[i], xv);
@@ -383,7 +385,7 @@ ln_bwd_fused_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TP*
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int64_t vi = lane + 32 * i;
-    const bool has = vi < nvec;
+    const bool has = FULL || vi < nvec;
 #pragma unroll
     for (int step = 1; step < FB_WARPS; step <<= 1) {
       float* slot = sh_fold + (warp / (2 * step)) * (NS * 32 * V);
@@ -560,10 +562,18 @@ cudaError_t ln_bwd_dispatch(const void* x, const void* dy, const void* gamma, co
     const unsigned grid = (unsigned)(want < FB_MAX_BLOCKS ? want : FB_MAX_BLOCKS);
     const size_t smem = 0;
 #define LT_LN_FUSED(NVV, DXSV)                                                                \
-  launch_pdl(ln_bwd_fused_kernel<T, TP, NVV, DXSV>, dim3(grid), dim3(FB_THREADS), smem, s,       \
-             (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add, (T*)dx,  \
-             rows, cols, scratch)
+  do {                                                                                           \
+    if (full_ok && cols == (int64_t)(NVV) * 32 * V)                                                \
+      launch_pdl(ln_bwd_fused_kernel<T, TP, NVV, DXSV, true>, dim3(grid), dim3(FB_THREADS), smem, s, \
+                 (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add,       \
+                 (T*)dx, rows, cols, scratch);                                                    \
+    else                                                                                         \
+      launch_pdl(ln_bwd_fused_kernel<T, TP, NVV, DXSV, false>, dim3(grid), dim3(FB_THREADS), smem, s, \
+                 (const T*)x, (const T*)dy, (const TP*)gamma, mean, rstd, (const T*)dx_add,       \
+                 (T*)dx, rows, cols, scratch);                                                    \
+  } while (0)
     const int64_t per_lane = (cols / V + 31) / 32;
+    static const bool full_ok = [] { const char* e = getenv("LT_LN_FULL"); return !(e && e[0] == '0'); }();
     const bool dxs = want_dxsum && per_lane <= 3;   // a third register set fits up to 3 vectors a lane
     if (dxs) {
       if (per_lane <= 1) LT_LN_FUSED(1, true);
